@@ -1,0 +1,9 @@
+"""B200-native CASTLE attention (causal attention with lookahead keys).
+
+`Castle` is a drop-in for `lookahead_keys_attention.Castle`; `castle_attention`
+replaces the reference's `castle_attention_triton` operator.
+"""
+from .castle import Cache, Castle
+from .ops import castle_attention, castle_decode_step, check_status
+
+__all__ = ["Castle", "Cache", "castle_attention", "castle_decode_step", "check_status"]

@@ -1,0 +1,321 @@
+// Cached single-token CASTLE step (HBM-bound).
+//
+// Per (batch, head) the step streams four caches of `t` rows once: it reads
+// qu_cache, U, kc_cache and vc_cache and writes U back, i.e. 5*t*d elements,
+// which is the algorithmic traffic of the step.  Each row is handled by d/VEC
+// adjacent lanes (VEC = 16 bytes of elements per lane), so every global access
+// is a 128-bit load/store and a warp touches whole 128-byte lines; the three
+// dot products of a row are reduced with xor-shuffles inside that lane group.
+// Rows are split over `nsplit` CTAs per (batch, head); each CTA keeps a running
+// (max, sum, weighted value sum) and writes one partial, which a small second
+// kernel merges.
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace castle {
+
+struct DecodeParams {
+  castle_tensor_t qc, kc, vc, qu, ku, vu;          // new rows
+  castle_tensor_t U, quc, kcc, vcc;                // caches
+  castle_tensor_t out;
+  float* part;                                     // [BH][nsplit][2 + D]
+  int H, t, nsplit, rows_per_split;
+  float scale;
+};
+
+template <typename T> struct Vec;  // 16 bytes of T <-> floats
+template <> struct Vec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+  static __device__ __forceinline__ void round(float*) {}
+};
+template <typename T> struct Vec16 {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const T* p, float* v) {
+    uint4 q = *reinterpret_cast<const uint4*>(p);
+    float2 a = Elem<T>::unpack2(q.x), b = Elem<T>::unpack2(q.y), c = Elem<T>::unpack2(q.z), d = Elem<T>::unpack2(q.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  }
+  static __device__ __forceinline__ void store(T* p, const float* v) {
+    uint4 q;
+    q.x = Elem<T>::pack2(v[0], v[1]); q.y = Elem<T>::pack2(v[2], v[3]);
+    q.z = Elem<T>::pack2(v[4], v[5]); q.w = Elem<T>::pack2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = q;
+  }
+  // round to the storage type, so the value used for the score equals the value stored
+  static __device__ __forceinline__ void round(float* v) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = Elem<T>::to_f(Elem<T>::from_f(v[i]));
+  }
+};
+template <> struct Vec<__nv_bfloat16> : Vec16<__nv_bfloat16> {};
+template <> struct Vec<__half> : Vec16<__half> {};
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+
+template <int LPR>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+constexpr int kDecodeThreads = 256;
+constexpr int kDecodeUnroll = 4;
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kDecodeThreads, 2) castle_decode_kernel(const DecodeParams p) {
+  constexpr int VEC = Vec<T>::N;
+  constexpr int LPR = D / VEC;                 // lanes per row
+  constexpr int RPW = 32 / LPR;                // rows per warp per pass
+  constexpr int NW = kDecodeThreads / 32;
+  const int bh = blockIdx.x, split = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LPR, grp = lane / LPR;
+  const int64_t col = (int64_t)sub * VEC;
+
+  auto row_ptr = [&](const castle_tensor_t& t, int64_t r) {
+    return reinterpret_cast<T*>(t.ptr) + b * t.stride_b + h * t.stride_h + r * t.stride_n + col;
+  };
+
+  float qcv[VEC], kuv[VEC], vuv[VEC];
+  Vec<T>::load(row_ptr(p.qc, 0), qcv);
+  Vec<T>::load(row_ptr(p.ku, 0), kuv);
+  Vec<T>::load(row_ptr(p.vu, 0), vuv);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) { qcv[i] *= p.scale; kuv[i] *= p.scale; }  // scale*(qu.ku) == qu.(scale*ku)
+
+  float m = -INFINITY, l = 0.f, acc[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+
+  const int r_begin = split * p.rows_per_split;
+  const int r_end = min(p.t, r_begin + p.rows_per_split);
+
+  // rows of this CTA, RPW*NW*UNROLL per pass
+  // (the loop bound is warp-uniform: the shuffles below need every lane of the warp)
+  for (int base = r_begin + warp * RPW; base < r_end; base += RPW * NW * kDecodeUnroll) {
+    float quv[kDecodeUnroll][VEC], uv[kDecodeUnroll][VEC], kv[kDecodeUnroll][VEC], vv[kDecodeUnroll][VEC];
+    bool live[kDecodeUnroll];
+#pragma unroll
+    for (int u = 0; u < kDecodeUnroll; ++u) {
+      int r = base + grp + u * RPW * NW;
+      live[u] = r < r_end;
+      if (live[u]) {
+        Vec<T>::load(row_ptr(p.quc, r), quv[u]);
+        Vec<T>::load(row_ptr(p.U, r), uv[u]);
+        Vec<T>::load(row_ptr(p.kcc, r), kv[u]);
+        Vec<T>::load(row_ptr(p.vcc, r), vv[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kDecodeUnroll; ++u) {
+      int r = base + grp + u * RPW * NW;
+      float z = 0.f, sc = 0.f, su = 0.f;
+      if (live[u]) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) z += quv[u][i] * kuv[i];
+      }
+      z = group_sum<LPR>(z);
+      float a = sigmoid_f(z);
+      if (live[u]) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) uv[u][i] += a * vuv[i];
+        Vec<T>::round(uv[u]);
+        Vec<T>::store(row_ptr(p.U, r), uv[u]);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) { sc += qcv[i] * kv[u][i]; su += qcv[i] * uv[u][i]; }
+      }
+      sc = group_sum<LPR>(sc);
+      su = group_sum<LPR>(su);
+      if (live[u]) {
+        float s = sc - su * sigmoid_f(su);
+        float mn = fmaxf(m, s);
+        float corr = __expf(m - mn), pe = __expf(s - mn);
+        l = l * corr + pe;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = acc[i] * corr + pe * vv[u][i];
+        m = mn;
+      }
+    }
+  }
+
+  // the appended row: U[t] = 0 so its score is just qc.kc_new; done by the last split
+  if (split == p.nsplit - 1 && warp == 0) {  // whole warp runs the shuffle; lane group 0 keeps the result
+    float kn[VEC], vn[VEC], qn[VEC], zero[VEC];
+    Vec<T>::load(row_ptr(p.kc, 0), kn);
+    Vec<T>::load(row_ptr(p.vc, 0), vn);
+    Vec<T>::load(row_ptr(p.qu, 0), qn);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) zero[i] = 0.f;
+    if (grp == 0) {
+      Vec<T>::store(row_ptr(p.kcc, p.t), kn);
+      Vec<T>::store(row_ptr(p.vcc, p.t), vn);
+      Vec<T>::store(row_ptr(p.quc, p.t), qn);
+      Vec<T>::store(row_ptr(p.U, p.t), zero);
+    }
+    float sc = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sc += qcv[i] * kn[i];
+    sc = group_sum<LPR>(sc);
+    if (grp == 0) {
+      float mn = fmaxf(m, sc);
+      float corr = __expf(m - mn), pe = __expf(sc - mn);
+      l = l * corr + pe;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = acc[i] * corr + pe * vn[i];
+      m = mn;
+    }
+  }
+
+  // merge the RPW lane groups of a warp, then the warps of the CTA
+#pragma unroll
+  for (int o = LPR; o < 32; o <<= 1) {
+    float m2 = __shfl_xor_sync(0xffffffffu, m, o), l2 = __shfl_xor_sync(0xffffffffu, l, o);
+    float mn = fmaxf(m, m2);
+    float c1 = (m == -INFINITY) ? 0.f : __expf(m - mn), c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+    l = l * c1 + l2 * c2;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      float a2 = __shfl_xor_sync(0xffffffffu, acc[i], o);
+      acc[i] = acc[i] * c1 + a2 * c2;
+    }
+    m = mn;
+  }
+  __shared__ float s_m[NW], s_l[NW], s_acc[NW][D];
+  if (grp == 0) {
+    if (sub == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) s_acc[warp][sub * VEC + i] = acc[i];
+  }
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) mm = fmaxf(mm, s_m[w]);
+    float ll = 0.f, aa = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      float c = (s_m[w] == -INFINITY) ? 0.f : __expf(s_m[w] - mm);
+      ll += s_l[w] * c;
+      aa += s_acc[w][threadIdx.x] * c;
+    }
+    if (p.nsplit == 1) {
+      T* o = reinterpret_cast<T*>(p.out.ptr) + b * p.out.stride_b + h * p.out.stride_h;
+      if constexpr (sizeof(T) == 4) o[threadIdx.x] = aa / ll;
+      else o[threadIdx.x] = Elem<T>::from_f(aa / ll);
+    } else {
+      float* dst = p.part + ((int64_t)bh * p.nsplit + split) * (2 + D);
+      if (threadIdx.x == 0) { dst[0] = mm; dst[1] = ll; }
+      dst[2 + threadIdx.x] = aa;
+    }
+  }
+}
+
+template <typename T, int D>
+__global__ void castle_decode_merge_kernel(const DecodeParams p) {
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H, c = threadIdx.x;
+  const float* src = p.part + (int64_t)bh * p.nsplit * (2 + D);
+  float mm = -INFINITY;
+  for (int s = 0; s < p.nsplit; ++s) mm = fmaxf(mm, src[s * (2 + D)]);
+  float ll = 0.f, aa = 0.f;
+  for (int s = 0; s < p.nsplit; ++s) {
+    float ms = src[s * (2 + D)];
+    float w = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+    ll += src[s * (2 + D) + 1] * w;
+    aa += src[s * (2 + D) + 2 + c] * w;
+  }
+  T* o = reinterpret_cast<T*>(p.out.ptr) + b * p.out.stride_b + h * p.out.stride_h;
+  if constexpr (sizeof(T) == 4) o[c] = aa / ll;
+  else o[c] = Elem<T>::from_f(aa / ll);
+}
+
+// Rows are split so that the grid has a few CTAs per SM even when batch*heads is small.
+static int decode_nsplit(int BH, int t) {
+  const int target_ctas = 148 * 4;
+  int ns = (target_ctas + BH - 1) / BH;
+  int max_by_rows = (t + 255) / 256;  // at least 256 rows per split
+  if (ns > max_by_rows) ns = max_by_rows;
+  if (ns < 1) ns = 1;
+  if (ns > 64) ns = 64;
+  return ns;
+}
+
+template <typename T, int D>
+static int launch_decode(const DecodeParams& p, int BH, cudaStream_t st) {
+  dim3 grid(BH, p.nsplit);
+  castle_decode_kernel<T, D><<<grid, kDecodeThreads, 0, st>>>(p);
+  if (p.nsplit > 1) castle_decode_merge_kernel<T, D><<<BH, D, 0, st>>>(p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : cuda_fail(e, "castle_decode_step launch");
+}
+
+template <typename T>
+static int launch_decode_d(const DecodeParams& p, int BH, int D, cudaStream_t st) {
+  switch (D) {
+    case 16: return launch_decode<T, 16>(p, BH, st);
+    case 32: return launch_decode<T, 32>(p, BH, st);
+    case 64: return launch_decode<T, 64>(p, BH, st);
+    case 128: return launch_decode<T, 128>(p, BH, st);
+  }
+  return reject("castle_decode_step: dim_head %d not supported (16, 32, 64, 128)", D);
+}
+
+}  // namespace castle
+
+using namespace castle;
+
+extern "C" size_t castle_decode_workspace_bytes(const castle_problem_t* p, int32_t cache_len) {
+  if (!p) return 0;
+  int BH = p->batch * p->heads;
+  return (size_t)BH * decode_nsplit(BH, cache_len) * (2 + p->dim_head) * sizeof(float);
+}
+
+extern "C" int castle_decode_step(const castle_problem_t* p, int32_t cache_len, int32_t capacity,
+                                  const castle_tensor_t* qc_new, const castle_tensor_t* kc_new,
+                                  const castle_tensor_t* vc_new, const castle_tensor_t* qu_new,
+                                  const castle_tensor_t* ku_new, const castle_tensor_t* vu_new,
+                                  const castle_tensor_t* u_cache, const castle_tensor_t* qu_cache,
+                                  const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache,
+                                  const castle_tensor_t* out, void* workspace, size_t workspace_bytes,
+                                  int32_t* status, void* stream) {
+  (void)status;
+  if (!p) return reject("castle_decode_step: null problem");
+  if (p->batch <= 0 || p->heads <= 0) return reject("castle_decode_step: empty batch/heads");
+  if (cache_len < 0 || cache_len >= capacity)
+    return reject("castle_decode_step: cache_len %d must be in [0, capacity %d)", cache_len, capacity);
+  if (p->dtype != CASTLE_BF16 && p->dtype != CASTLE_F16 && p->dtype != CASTLE_F32)
+    return reject("castle_decode_step: unknown dtype %d", p->dtype);
+  int rc = 0;
+  const castle_tensor_t* ts[11] = {qc_new, kc_new, vc_new, qu_new, ku_new, vu_new, u_cache, qu_cache, kc_cache, vc_cache, out};
+  const char* names[11] = {"qc_new", "kc_new", "vc_new", "qu_new", "ku_new", "vu_new", "u_cache", "qu_cache", "kc_cache", "vc_cache", "out"};
+  for (int i = 0; i < 11; ++i)
+    if (!tensor_ok(ts[i], p->dtype, names[i], &rc)) return rc;
+  DecodeParams dp;
+  dp.qc = *qc_new; dp.kc = *kc_new; dp.vc = *vc_new; dp.qu = *qu_new; dp.ku = *ku_new; dp.vu = *vu_new;
+  dp.U = *u_cache; dp.quc = *qu_cache; dp.kcc = *kc_cache; dp.vcc = *vc_cache; dp.out = *out;
+  int BH = p->batch * p->heads;
+  dp.H = p->heads; dp.t = cache_len; dp.scale = p->scale;
+  dp.nsplit = decode_nsplit(BH, cache_len);
+  dp.rows_per_split = (cache_len + dp.nsplit - 1) / dp.nsplit;
+  if (dp.rows_per_split < 1) dp.rows_per_split = 1;
+  dp.part = (float*)workspace;
+  if (dp.nsplit > 1) {
+    size_t need = (size_t)BH * dp.nsplit * (2 + p->dim_head) * sizeof(float);
+    if (!workspace || workspace_bytes < need)
+      return reject("castle_decode_step: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (p->dtype) {
+    case CASTLE_BF16: return launch_decode_d<__nv_bfloat16>(dp, BH, p->dim_head, st);
+    case CASTLE_F16: return launch_decode_d<__half>(dp, BH, p->dim_head, st);
+    default: return launch_decode_d<float>(dp, BH, p->dim_head, st);
+  }
+}

@@ -1,0 +1,449 @@
+// CASTLE parallel forward for sm_100a.
+//
+// The reference evaluates Su = T @ A^T as an (N x N) x (N x N) product, O(N^3)
+// per head.  Here each CTA owns one block K of 128 keys and walks the query
+// blocks I = K, K+1, ... keeping the running lookahead state
+//     W_K = sum_{J < I} A[K,J] @ Vu[J]          (128 x d, fp32, in tensor memory)
+// so that
+//     Su[I,K] = Qc[I] @ W_K^T + tril(T[I,I]) @ A[K,I]^T
+// costs O(N^2 d) in total.  Per (I,K) step the CTA issues seven tcgen05 products
+// (Z, W update, T, Su main, Su in-block term, Sc, P@Vc), all with fp32
+// accumulators in TMEM and 16-bit operands in 128-byte-swizzled shared memory,
+// either loaded by TMA (inputs) or written by the threads (sigmoid gate A,
+// masked T, the 16-bit copy of W, soft-max numerators P).  Thread r of the CTA
+// owns row r of every accumulator, so row maxima and sums need no shuffles.
+//
+// The soft-max over keys crosses CTAs, so each step emits an un-normalised
+// partial (row max, row sum, P@Vc) and a second kernel merges the partials of a
+// query block.  After the last step W_K is exactly U[K], the lookahead keys the
+// decode cache stores, and (unrounded) the state the backward starts from.
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace castle {
+
+constexpr int kBlk = 128;                       // keys per CTA, queries per step
+constexpr uint32_t kPanelBytes = kBlk * 128;    // [128 rows][64 x 16-bit]
+
+struct FwdParams {
+  int B, H, N, nblk;
+  float scale;
+  float* part_ml;   // [BH][ntiles][128][2]
+  float* part_o;    // [BH][ntiles][128][D]
+  float* lse;       // [BH][N]
+  float* w_state;   // [BH][N][D] or null
+  castle_tensor_t u_out;  // ptr may be null
+  int u_dtype;
+  castle_tensor_t out;
+  int32_t* status;
+};
+
+__host__ __device__ inline int64_t tri(int64_t i) { return i * (i + 1) / 2; }
+
+__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128, 1)
+castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
+                  const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
+                  const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu) {
+  constexpr int NP = D / 64;                         // panels per d-wide operand
+  constexpr uint32_t OPB = NP * kPanelBytes;         // bytes of a d-wide operand tile
+  constexpr uint32_t SQB = 2 * kPanelBytes;          // bytes of a 128x128 tile
+  constexpr uint32_t TM_COLS = (D == 64) ? 256 : 512;
+  constexpr uint32_t COL_W = 0, COL_S = D, COL_O = D + 128;
+  constexpr int FMT = Elem<T>::fmt;
+  constexpr uint32_t ID_SQ = make_idesc(128, 128, FMT, false, false, false);
+  constexpr uint32_t ID_D = make_idesc(128, D, FMT, false, true, false);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQu = smem;
+  uint8_t* sKc = sQu + OPB;
+  uint8_t* sVc = sKc + OPB;
+  uint8_t* sQc = sVc + OPB;
+  uint8_t* sWb = sQc + OPB;
+  uint8_t* sKuA = sWb + OPB;   // Ku[I], then the gate A[K,I], then the soft-max numerators P
+  uint8_t* sVuT = sKuA + SQB;  // Vu[I], then the masked T[I,I]
+  __shared__ uint64_t bar_res, bar_load, bar_mma;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int bh = blockIdx.x, K = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int k0 = K * kBlk;
+
+  if (tid == 0) {
+    mbar_init(&bar_res, 1);
+    mbar_init(&bar_load, 1);
+    mbar_init(&bar_mma, 1);
+    mbar_fence_init();
+    abort_flag = 0;
+    tma_prefetch_desc(&m_qc); tma_prefetch_desc(&m_ku); tma_prefetch_desc(&m_vu);
+  }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, TM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
+  volatile int* abortp = &abort_flag;
+
+  if (tid == 0) {
+    mbar_expect_tx(&bar_res, 3 * OPB);
+#pragma unroll
+    for (int pn = 0; pn < NP; ++pn) {
+      tma_load_4d(sQu + pn * kPanelBytes, &m_qu, &bar_res, pn * 64, k0, h, b);
+      tma_load_4d(sKc + pn * kPanelBytes, &m_kc, &bar_res, pn * 64, k0, h, b);
+      tma_load_4d(sVc + pn * kPanelBytes, &m_vc, &bar_res, pn * 64, k0, h, b);
+    }
+  }
+  mbar_wait(&bar_res, 0, abortp);
+
+  uint32_t ph_load = 0, ph_mma = 0;
+  const uint32_t aQu = smem_u32(sQu), aKc = smem_u32(sKc), aVc = smem_u32(sVc), aQc = smem_u32(sQc),
+                 aWb = smem_u32(sWb), aKuA = smem_u32(sKuA), aVuT = smem_u32(sVuT);
+  const int krow = k0 + tid;  // global key index of this thread's row when rows are keys
+
+  for (int I = K; I < p.nblk; ++I) {
+    const int i0 = I * kBlk;
+    const bool diag = (I == K);
+    // ---- stream in Qc[I], Ku[I], Vu[I]
+    if (tid == 0) {
+      mbar_expect_tx(&bar_load, 3 * OPB);
+#pragma unroll
+      for (int pn = 0; pn < NP; ++pn) {
+        tma_load_4d(sQc + pn * kPanelBytes, &m_qc, &bar_load, pn * 64, i0, h, b);
+        tma_load_4d(sKuA + pn * kPanelBytes, &m_ku, &bar_load, pn * 64, i0, h, b);
+        tma_load_4d(sVuT + pn * kPanelBytes, &m_vu, &bar_load, pn * 64, i0, h, b);
+      }
+    }
+    mbar_wait(&bar_load, ph_load, abortp);
+    ph_load ^= 1;
+
+    // ---- Z[K,I] = Qu[K] @ Ku[I]^T  (rows = keys k, columns = positions j)
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_kk(tmem + COL_S, aQu, kPanelBytes, aKuA, kPanelBytes, NP, ID_SQ, false);
+      mma_commit(&bar_mma);
+    }
+    mbar_wait(&bar_mma, ph_mma, abortp);
+    ph_mma ^= 1;
+    tc_fence_after();
+    // gate A = sigmoid(scale * Z), kept for j > k; written over Ku[I]
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float v[32];
+      tmem_ld32(trow + COL_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float a = sigmoidf_fast(v[j] * p.scale);
+        v[j] = (!diag || (i0 + c * 32 + j > krow)) ? a : 0.f;
+      }
+      store_row32<T>(sKuA, kPanelBytes, tid, c * 32, v);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- W_K += A @ Vu[I]   and   T[I,I] = Qc[I] @ Vu[I]^T
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_km(tmem + COL_W, aKuA, kPanelBytes, aVuT, kPanelBytes, 8, ID_D, !diag);
+      gemm_kk(tmem + COL_S, aQc, kPanelBytes, aVuT, kPanelBytes, NP, ID_SQ, false);
+      mma_commit(&bar_mma);
+    }
+    mbar_wait(&bar_mma, ph_mma, abortp);
+    ph_mma ^= 1;
+    tc_fence_after();
+    // masked T (j <= i), unscaled, written over Vu[I]
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float v[32];
+      tmem_ld32(trow + COL_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j <= tid) ? v[j] : 0.f;
+      store_row32<T>(sVuT, kPanelBytes, tid, c * 32, v);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- Su/scale = Qc[I] @ Wb^T + Tm @ A^T   (Wb = 16-bit copy of W before this step's update)
+    if (tid == 0) {
+      tc_fence_after();
+      if (!diag) gemm_kk(tmem + COL_S, aQc, kPanelBytes, aWb, kPanelBytes, NP, ID_SQ, false);
+      gemm_kk(tmem + COL_S, aVuT, kPanelBytes, aKuA, kPanelBytes, 2, ID_SQ, !diag);
+      mma_commit(&bar_mma);
+    }
+    mbar_wait(&bar_mma, ph_mma, abortp);
+    ph_mma ^= 1;
+    tc_fence_after();
+    // penalty -silu(Su)/scale goes back into the accumulator; Sc is then accumulated on top of it
+    const float inv_scale = 1.f / p.scale;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float v[32];
+      tmem_ld32(trow + COL_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float su = v[j] * p.scale;
+        v[j] = -su * sigmoidf_fast(su) * inv_scale;
+      }
+      tmem_st32(trow + COL_S + c * 32, v);
+    }
+    // refresh the 16-bit copy of W (now including block I) for the next step
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      float v[32];
+      tmem_ld32(trow + COL_W + c * 32, v);
+      tmem_ld_wait();
+      store_row32<T>(sWb, kPanelBytes, tid, c * 32, v);
+    }
+    tmem_st_wait();
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- S/scale = penalty + Qc[I] @ Kc[K]^T
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_kk(tmem + COL_S, aQc, kPanelBytes, aKc, kPanelBytes, NP, ID_SQ, true);
+      mma_commit(&bar_mma);
+    }
+    mbar_wait(&bar_mma, ph_mma, abortp);
+    ph_mma ^= 1;
+    tc_fence_after();
+    // row max, then P = exp(S - max) (rows = queries i, columns = keys k)
+    const int irow = i0 + tid;
+    float mrow = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float v[32];
+      tmem_ld32(trow + COL_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        bool ok = !diag || (c * 32 + j <= tid);
+        mrow = fmaxf(mrow, ok ? v[j] * p.scale : -INFINITY);
+      }
+    }
+    float lrow = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      float v[32];
+      tmem_ld32(trow + COL_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        bool ok = !diag || (c * 32 + j <= tid);
+        float pe = ok ? __expf(v[j] * p.scale - mrow) : 0.f;
+        lrow += pe;
+        v[j] = pe;
+      }
+      store_row32<T>(sKuA, kPanelBytes, tid, c * 32, v);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- O_partial = P @ Vc[K]
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_km(tmem + COL_O, aKuA, kPanelBytes, aVc, kPanelBytes, 8, ID_D, false);
+      mma_commit(&bar_mma);
+    }
+    const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;
+    if (irow < p.N) {
+      float2* ml = reinterpret_cast<float2*>(p.part_ml) + tile * kBlk + tid;
+      *ml = make_float2(mrow, lrow);
+    }
+    mbar_wait(&bar_mma, ph_mma, abortp);
+    ph_mma ^= 1;
+    tc_fence_after();
+    {
+      float* dst = p.part_o + (tile * kBlk + tid) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        float v[32];
+        tmem_ld32(trow + COL_O + c * 32, v);
+        tmem_ld_wait();
+        if (irow < p.N) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        }
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+  }
+
+  // ---- W_K is now U[K]: the cache's lookahead keys and the backward's starting state
+  if (p.u_out.ptr != nullptr || p.w_state != nullptr) {
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      float v[32];
+      tmem_ld32(trow + COL_W + c * 32, v);
+      tmem_ld_wait();
+      if (krow < p.N) {
+        if (p.w_state != nullptr) {
+          float* dst = p.w_state + ((int64_t)bh * p.N + krow) * D + c * 32;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        }
+        if (p.u_out.ptr != nullptr) {
+          int64_t off = b * p.u_out.stride_b + h * p.u_out.stride_h + (int64_t)krow * p.u_out.stride_n + c * 32;
+          if (p.u_dtype == CASTLE_F32) {
+            float* dst = reinterpret_cast<float*>(p.u_out.ptr) + off;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else if (p.u_dtype == CASTLE_BF16) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.u_out.ptr) + off);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              dst[j] = make_uint4(Elem<__nv_bfloat16>::pack2(v[8 * j], v[8 * j + 1]),
+                                  Elem<__nv_bfloat16>::pack2(v[8 * j + 2], v[8 * j + 3]),
+                                  Elem<__nv_bfloat16>::pack2(v[8 * j + 4], v[8 * j + 5]),
+                                  Elem<__nv_bfloat16>::pack2(v[8 * j + 6], v[8 * j + 7]));
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.u_out.ptr) + off);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              dst[j] = make_uint4(Elem<__half>::pack2(v[8 * j], v[8 * j + 1]),
+                                  Elem<__half>::pack2(v[8 * j + 2], v[8 * j + 3]),
+                                  Elem<__half>::pack2(v[8 * j + 4], v[8 * j + 5]),
+                                  Elem<__half>::pack2(v[8 * j + 6], v[8 * j + 7]));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TM_COLS);
+  if (tid == 0 && abort_flag) atomicOr(p.status, CASTLE_STATUS_WAIT_TIMEOUT);
+}
+
+// Merge the per-key-block partials of one query block: out = sum_K e^{m_K - m} O_K / sum_K e^{m_K - m} l_K.
+// D/4 threads per row, each owning one float4 of the row.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) castle_fwd_merge_kernel(const FwdParams p) {
+  constexpr int TPR = D / 4, ROWS = 256 / TPR;
+  const int bh = blockIdx.y, I = blockIdx.x / (kBlk / ROWS), sub = blockIdx.x % (kBlk / ROWS);
+  const int r = sub * ROWS + threadIdx.x / TPR, c4 = threadIdx.x % TPR;
+  const int i = I * kBlk + r;
+  if (i >= p.N) return;
+  const int64_t tile0 = (int64_t)bh * tri(p.nblk) + tri(I);
+  const float2* ml = reinterpret_cast<const float2*>(p.part_ml) + tile0 * kBlk + r;
+  float m = -INFINITY;
+  for (int K = 0; K <= I; ++K) m = fmaxf(m, ml[(int64_t)K * kBlk].x);
+  float l = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* po = reinterpret_cast<const float4*>(p.part_o + (tile0 * kBlk + r) * D) + c4;
+  for (int K = 0; K <= I; ++K) {
+    float2 v = ml[(int64_t)K * kBlk];
+    float w = __expf(v.x - m);
+    l += v.y * w;
+    float4 o = po[(int64_t)K * kBlk * D / 4];
+    acc.x += o.x * w; acc.y += o.y * w; acc.z += o.z * w; acc.w += o.w * w;
+  }
+  const float inv = 1.f / l;
+  const int b = bh / p.H, h = bh % p.H;
+  T* dst = reinterpret_cast<T*>(p.out.ptr) + b * p.out.stride_b + h * p.out.stride_h + (int64_t)i * p.out.stride_n + c4 * 4;
+  uint2 q;
+  q.x = Elem<T>::pack2(acc.x * inv, acc.y * inv);
+  q.y = Elem<T>::pack2(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(dst) = q;
+  if (c4 == 0) p.lse[(int64_t)bh * p.N + i] = m + __logf(l);
+}
+
+template <typename T, int D>
+static int launch_fwd(const FwdParams& p, const CUtensorMap* maps, cudaStream_t st) {
+  constexpr size_t smem = 5 * (D / 64) * kPanelBytes + 2 * 2 * kPanelBytes + 1024;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(castle_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e, "castle_fwd attribute");
+    attr_done = true;
+  }
+  dim3 grid(p.B * p.H, p.nblk);
+  castle_fwd_kernel<T, D><<<grid, 128, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+  constexpr int ROWS = 256 / (D / 4);
+  dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);
+  castle_fwd_merge_kernel<T, D><<<g2, 256, 0, st>>>(p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : cuda_fail(e, "castle_fwd launch");
+}
+
+static int check_parallel_problem(const castle_problem_t* p, const char* who) {
+  if (!p) return reject("%s: null problem", who);
+  if (p->batch <= 0 || p->heads <= 0 || p->seq_len <= 0) return reject("%s: empty problem", who);
+  if (p->dim_head != 64 && p->dim_head != 128) return reject("%s: dim_head %d not supported (64 or 128)", who, p->dim_head);
+  if (p->dtype != CASTLE_BF16 && p->dtype != CASTLE_F16) return reject("%s: dtype %d not supported (bf16, fp16)", who, p->dtype);
+  if ((int64_t)p->batch * p->heads > 2147483647LL || (p->seq_len + kBlk - 1) / kBlk > 65535)
+    return reject("%s: grid too large", who);
+  return 0;
+}
+
+}  // namespace castle
+
+using namespace castle;
+
+extern "C" size_t castle_fwd_workspace_bytes(const castle_problem_t* p) {
+  if (!p || p->seq_len <= 0) return 0;
+  int64_t nb = (p->seq_len + kBlk - 1) / kBlk;
+  int64_t tiles = (int64_t)p->batch * p->heads * tri(nb);
+  return (size_t)(tiles * kBlk * (2 + p->dim_head) * sizeof(float));
+}
+
+extern "C" int castle_fwd(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
+                          const castle_tensor_t* vc, const castle_tensor_t* qu, const castle_tensor_t* ku,
+                          const castle_tensor_t* vu, const castle_tensor_t* out, float* lse,
+                          const castle_tensor_t* u_out, int32_t u_dtype, float* w_state, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream) {
+  int rc = check_parallel_problem(p, "castle_fwd");
+  if (rc) return rc;
+  const castle_tensor_t* ins[6] = {qc, kc, vc, qu, ku, vu};
+  const char* names[6] = {"qc", "kc", "vc", "qu", "ku", "vu"};
+  for (int i = 0; i < 6; ++i)
+    if (!tensor_ok(ins[i], p->dtype, names[i], &rc)) return rc;
+  if (!tensor_ok(out, p->dtype, "out", &rc)) return rc;
+  if (!lse || !status) return reject("castle_fwd: lse and status must not be null");
+  if (u_out && u_out->ptr) {
+    if (u_dtype != CASTLE_BF16 && u_dtype != CASTLE_F16 && u_dtype != CASTLE_F32) return reject("castle_fwd: bad u_dtype");
+    if (!tensor_ok(u_out, u_dtype, "u_out", &rc)) return rc;
+  }
+  size_t need = castle_fwd_workspace_bytes(p);
+  if (!workspace || workspace_bytes < need)
+    return reject("castle_fwd: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
+  if (((uintptr_t)workspace) % 16) return reject("castle_fwd: workspace not 16-byte aligned");
+
+  FwdParams fp;
+  fp.B = p->batch; fp.H = p->heads; fp.N = p->seq_len; fp.nblk = (p->seq_len + kBlk - 1) / kBlk;
+  fp.scale = p->scale;
+  int64_t tiles = (int64_t)p->batch * p->heads * tri(fp.nblk);
+  fp.part_ml = (float*)workspace;
+  fp.part_o = fp.part_ml + tiles * kBlk * 2;
+  fp.lse = lse; fp.w_state = w_state;
+  fp.u_out = (u_out && u_out->ptr) ? *u_out : castle_tensor_t{nullptr, 0, 0, 0};
+  fp.u_dtype = u_dtype;
+  fp.out = *out; fp.status = status;
+
+  CUtensorMap maps[6];
+  for (int i = 0; i < 6; ++i) {
+    rc = make_tmap_16bit(&maps[i], ins[i], p->dtype, p->batch, p->heads, p->seq_len, p->dim_head, kBlk, names[i]);
+    if (rc) return rc;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p->dtype == CASTLE_BF16)
+    return p->dim_head == 64 ? launch_fwd<__nv_bfloat16, 64>(fp, maps, st) : launch_fwd<__nv_bfloat16, 128>(fp, maps, st);
+  return p->dim_head == 64 ? launch_fwd<__half, 64>(fp, maps, st) : launch_fwd<__half, 128>(fp, maps, st);
+}

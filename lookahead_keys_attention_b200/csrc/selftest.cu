@@ -1,0 +1,115 @@
+// Self test of the tensor-core building blocks: one 128x128x128 product through
+// every operand form the CASTLE kernels use (rows-contracted and
+// columns-contracted shared-memory operands, staged by thread stores or by TMA,
+// a preset accumulator and a negated operand).
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace castle {
+
+constexpr uint32_t kPanel = 128 * 128;  // bytes of a [128 rows][64 x 16-bit] panel
+
+__global__ void __launch_bounds__(128) castle_selftest_kernel(int mode, const __nv_bfloat16* x, const __nv_bfloat16* y,
+                                                              float* d, int32_t* status,
+                                                              const __grid_constant__ CUtensorMap mx,
+                                                              const __grid_constant__ CUtensorMap my) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sx = smem;               // 2 panels
+  uint8_t* sy = smem + 2 * kPanel;  // 2 panels
+  __shared__ uint64_t bar_tma, bar_mma;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const bool use_tma = mode >= 5;
+  const int op = use_tma ? mode - 5 : mode;
+
+  if (tid == 0) {
+    mbar_init(&bar_tma, 1);
+    mbar_init(&bar_mma, 1);
+    mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 128); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+
+  if (use_tma) {
+    if (tid == 0) {
+      mbar_expect_tx(&bar_tma, 4 * kPanel);
+      tma_load_4d(sx, &mx, &bar_tma, 0, 0, 0, 0);
+      tma_load_4d(sx + kPanel, &mx, &bar_tma, 64, 0, 0, 0);
+      tma_load_4d(sy, &my, &bar_tma, 0, 0, 0, 0);
+      tma_load_4d(sy + kPanel, &my, &bar_tma, 64, 0, 0, 0);
+    }
+    mbar_wait(&bar_tma, 0, &abort_flag);
+  } else {
+    for (int c = 0; c < 16; ++c) {
+      uint4 vx = *reinterpret_cast<const uint4*>(x + tid * 128 + c * 8);
+      uint4 vy = *reinterpret_cast<const uint4*>(y + tid * 128 + c * 8);
+      *reinterpret_cast<uint4*>(sx + (c >> 3) * kPanel + swz_off(tid, c & 7)) = vx;
+      *reinterpret_cast<uint4*>(sy + (c >> 3) * kPanel + swz_off(tid, c & 7)) = vy;
+    }
+    fence_async_smem();
+  }
+  if (op == 4) {  // preset the accumulator to 1.0
+    float ones[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) ones[i] = 1.f;
+    for (int c = 0; c < 4; ++c) tmem_st32(tmem + ((uint32_t)(warp * 32) << 16) + c * 32, ones);
+    tmem_st_wait();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  if (tid == 0) {
+    const uint32_t xa = smem_u32(sx), ya = smem_u32(sy);
+    switch (op) {
+      case 0: gemm_kk(tmem, xa, kPanel, ya, kPanel, 2, make_idesc(128, 128, 1, false, false, false), false); break;
+      case 1: gemm_km(tmem, xa, kPanel, ya, kPanel, 8, make_idesc(128, 128, 1, false, true, false), false); break;
+      case 2: gemm_mm(tmem, xa, kPanel, ya, kPanel, 8, make_idesc(128, 128, 1, true, true, false), false); break;
+      case 3: gemm_mk(tmem, xa, kPanel, ya, kPanel, 8, make_idesc(128, 128, 1, true, false, false), false); break;
+      default: gemm_kk(tmem, xa, kPanel, ya, kPanel, 2, make_idesc(128, 128, 1, false, false, true), true); break;
+    }
+    mma_commit(&bar_mma);
+  }
+  mbar_wait(&bar_mma, 0, &abort_flag);
+  tc_fence_after();
+  for (int c = 0; c < 4; ++c) {
+    float v[32];
+    tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c * 32, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) d[tid * 128 + c * 32 + i] = v[i];
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 128);
+  if (tid == 0 && abort_flag) atomicOr(status, CASTLE_STATUS_WAIT_TIMEOUT);
+}
+
+}  // namespace castle
+
+using namespace castle;
+
+extern "C" int castle_selftest_mma(int32_t mode, const void* x, const void* y, float* d, int32_t* status,
+                                   void* stream) {
+  if (mode < 0 || mode > 8) return reject("castle_selftest_mma: mode %d out of range", mode);
+  if (!x || !y || !d || !status) return reject("castle_selftest_mma: null pointer");
+  CUtensorMap mx, my;
+  castle_tensor_t tx = {(void*)x, 128 * 128, 128 * 128, 128}, ty = {(void*)y, 128 * 128, 128 * 128, 128};
+  int rc = make_tmap_16bit(&mx, &tx, CASTLE_BF16, 1, 1, 128, 128, 128, "x");
+  if (rc) return rc;
+  rc = make_tmap_16bit(&my, &ty, CASTLE_BF16, 1, 1, 128, 128, 128, "y");
+  if (rc) return rc;
+  size_t smem = 4 * kPanel + 1024;
+  cudaError_t e = cudaFuncSetAttribute(castle_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return cuda_fail(e, "castle_selftest_mma attribute");
+  castle_selftest_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(mode, (const __nv_bfloat16*)x,
+                                                                 (const __nv_bfloat16*)y, d, status, mx, my);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : cuda_fail(e, "castle_selftest_mma launch");
+}

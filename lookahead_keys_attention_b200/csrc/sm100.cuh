@@ -1,0 +1,279 @@
+// Thin wrappers over the sm_100a instructions the CASTLE kernels are written in:
+// mbarrier, TMA tile loads (cp.async.bulk.tensor), tensor memory (TMEM)
+// allocation, tcgen05.mma with shared-memory operand descriptors, and
+// tcgen05.ld/st between TMEM and registers.
+//
+// Every wait is bounded.  A wait that runs out of polls raises a CTA-wide
+// abort flag in shared memory; from then on every wait in that CTA returns at
+// once, the kernel falls through its (bounded) loops, frees its TMEM and
+// records an error code in the status word the host reads back.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace castle {
+
+constexpr uint32_t kWaitPollLimit = 1u << 22;  // polls of mbarrier.try_wait before giving up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---------------------------------------------------------------- mbarrier
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kWaitPollLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (*abort_flag) return;
+  }
+  *abort_flag = 1;
+}
+
+// ---------------------------------------------------------------- fences
+__device__ __forceinline__ void fence_async_smem() {  // generic-proxy smem writes -> async proxy (MMA/TMA) reads
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// ---------------------------------------------------------------- TMA
+// 4-D tile load: coordinates are (c0 = element in row, c1 = row, c2 = head, c3 = batch).
+__device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
+      "[%2];" ::"r"(smem_u32(dst)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// ---------------------------------------------------------------- TMEM
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {  // whole warp
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {  // whole warp
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// ---------------------------------------------------------------- descriptors
+// Shared-memory operand tiles are [rows][64 x 16-bit] with 128-byte rows and the
+// 128-byte swizzle (16-byte chunk index XOR row%8), 1024-byte aligned: exactly
+// what a TMA load with SWIZZLE_128B and a 64-element inner box writes.  Wider
+// operands are several such "panels" laid one after another.
+constexpr uint32_t kPanelRowBytes = 128;
+
+__device__ __forceinline__ uint32_t swz_off(uint32_t row, uint32_t chunk16) {  // byte offset inside a panel
+  return row * kPanelRowBytes + ((chunk16 ^ (row & 7u)) << 4);
+}
+
+// Descriptor for a panel read along its rows (the contraction index runs inside a
+// row: "K-major").  8-row groups are 1024 bytes apart.  One MMA consumes 16
+// elements = 32 bytes of every row; step k adds 32*k bytes to the start address.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;                  // leading byte offset: unused for swizzled K-major
+  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                  // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
+  return d;
+}
+// Descriptor for panels read down their columns (the contraction index is the ROW,
+// the M/N index runs inside a row: "MN-major").  One MMA consumes 16 rows = two
+// 8-row groups (stride byte offset 1024); M/N beyond 64 continues in the next
+// panel, `panel_bytes` further on (leading byte offset).
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr, uint32_t panel_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((panel_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16 with fp32 accumulation.
+// fmt: 0 = fp16 operands, 1 = bf16 operands.
+__host__ __device__ constexpr uint32_t make_idesc(int M, int N, int fmt, bool a_mn, bool b_mn, bool neg_a) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((neg_a ? 1u : 0u) << 13) |
+         ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) |
+         ((uint32_t)(M >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"((uint32_t)accum)
+      : "memory");
+}
+// Make an mbarrier complete once every MMA this thread issued so far has finished.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// ---------------------------------------------------------------- TMEM <-> registers
+// Warp w of a 128-thread group touches lanes 32*(w%4)..+31; each thread gets 32
+// consecutive 32-bit columns of its own lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+      "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+      "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------- 16-bit element helpers
+template <typename T> struct Elem;
+template <> struct Elem<__nv_bfloat16> {
+  static constexpr int fmt = 1;
+  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+  }
+  static __device__ __forceinline__ float2 unpack2(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  }
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+};
+template <> struct Elem<__half> {
+  static constexpr int fmt = 0;
+  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __half2 p = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+  }
+  static __device__ __forceinline__ float2 unpack2(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+  static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+};
+
+// Write 32 consecutive elements (columns c0..c0+31, c0 a multiple of 32) of row `row`
+// of a swizzled panel set whose panels are `panel_bytes` apart.
+template <typename T>
+__device__ __forceinline__ void store_row32(uint8_t* tile, uint32_t panel_bytes, uint32_t row, uint32_t c0,
+                                            const float* v) {
+  uint8_t* panel = tile + (c0 >> 6) * panel_bytes;
+  uint32_t chunk0 = (c0 & 63u) >> 3;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 q;
+    q.x = Elem<T>::pack2(v[8 * c + 0], v[8 * c + 1]);
+    q.y = Elem<T>::pack2(v[8 * c + 2], v[8 * c + 3]);
+    q.z = Elem<T>::pack2(v[8 * c + 4], v[8 * c + 5]);
+    q.w = Elem<T>::pack2(v[8 * c + 6], v[8 * c + 7]);
+    *reinterpret_cast<uint4*>(panel + swz_off(row, chunk0 + c)) = q;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void load_row32(const uint8_t* tile, uint32_t panel_bytes, uint32_t row, uint32_t c0,
+                                           float* v) {
+  const uint8_t* panel = tile + (c0 >> 6) * panel_bytes;
+  uint32_t chunk0 = (c0 & 63u) >> 3;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint4 q = *reinterpret_cast<const uint4*>(panel + swz_off(row, chunk0 + c));
+    float2 a = Elem<T>::unpack2(q.x), b = Elem<T>::unpack2(q.y), e = Elem<T>::unpack2(q.z), f = Elem<T>::unpack2(q.w);
+    v[8 * c + 0] = a.x; v[8 * c + 1] = a.y; v[8 * c + 2] = b.x; v[8 * c + 3] = b.y;
+    v[8 * c + 4] = e.x; v[8 * c + 5] = e.y; v[8 * c + 6] = f.x; v[8 * c + 7] = f.y;
+  }
+}
+
+// ---------------------------------------------------------------- whole-tile MMA helpers (one issuing thread)
+// C[128 x N] (+)= X[128 x Kc] * Y[N x Kc]^T, both operands read along rows; Kc = 64*npanels.
+__device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
+                                        uint32_t y_panel_bytes, int npanels, uint32_t idesc, bool accum) {
+  for (int p = 0; p < npanels; ++p) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      mma_ss(d_tmem, desc_kmajor(x_addr + p * x_panel_bytes + 32 * k), desc_kmajor(y_addr + p * y_panel_bytes + 32 * k),
+             idesc, accum || p > 0 || k > 0);
+    }
+  }
+}
+// C[128 x N] (+)= X[128 x Kc] * Y[Kc x N]: X read along rows, Y ([Kc rows][N], panels of 64
+// columns `y_panel_bytes` apart) read down its columns.  Kc = 16*ksteps (rows of Y).
+__device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
+                                        uint32_t y_panel_bytes, int ksteps, uint32_t idesc, bool accum) {
+  for (int k = 0; k < ksteps; ++k) {
+    uint32_t xa = x_addr + (k >> 2) * x_panel_bytes + 32 * (k & 3);
+    mma_ss(d_tmem, desc_kmajor(xa), desc_mnmajor(y_addr + 2048 * k, y_panel_bytes), idesc, accum || k > 0);
+  }
+}
+// C[128 x N] (+)= X^T * Y with X [Kc rows][128] and Y [Kc rows][N], both read down their columns.
+__device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
+                                        uint32_t y_panel_bytes, int ksteps, uint32_t idesc, bool accum) {
+  for (int k = 0; k < ksteps; ++k) {
+    mma_ss(d_tmem, desc_mnmajor(x_addr + 2048 * k, x_panel_bytes), desc_mnmajor(y_addr + 2048 * k, y_panel_bytes),
+           idesc, accum || k > 0);
+  }
+}
+// C[128 x N] (+)= X^T * Y^T with X [Kc rows][128] read down its columns and Y [N rows][Kc] read along rows.
+__device__ __forceinline__ void gemm_mk(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
+                                        uint32_t y_panel_bytes, int ksteps, uint32_t idesc, bool accum) {
+  for (int k = 0; k < ksteps; ++k) {
+    uint32_t ya = y_addr + (k >> 2) * y_panel_bytes + 32 * (k & 3);
+    mma_ss(d_tmem, desc_mnmajor(x_addr + 2048 * k, x_panel_bytes), desc_kmajor(ya), idesc, accum || k > 0);
+  }
+}
+
+}  // namespace castle

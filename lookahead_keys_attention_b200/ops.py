@@ -1,0 +1,201 @@
+"""Operator layer: the CASTLE attention core as torch-facing functions that hand
+raw device pointers, strides and the current stream to the C-ABI library.
+
+`castle_attention` mirrors the reference operator
+`castle_attention_triton(qc, kc, vc, qu, ku, vu, scale, return_U_for_cache)`
+(lookahead_keys_attention/lookahead_keys_attention_triton.py:416-605): same
+argument order (causal triple first), unscaled inputs, returns `out` or
+`(out, U)`, six input gradients, no gradient through U.
+`castle_decode_step` replaces the single-token branch of the reference module
+(lookahead_keys_attention/lookahead_keys_attention.py:166-203).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from ._lib import CastleProblem, CastleTensor
+
+_DTYPES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
+
+_status_words: dict = {}
+_workspaces: dict = {}
+
+
+def _require_cuda(t: torch.Tensor, what: str):
+    if not t.is_cuda:
+        raise RuntimeError(f"{what}: expected CUDA tensors; this package has no CPU path")
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 the kernels OR error bits into (0 = fine)."""
+    device = torch.device(device)
+    w = _status_words.get(device)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[device] = w
+    return w
+
+
+def check_status(device=None):
+    """Synchronising check of the device status word; raises on a kernel-side failure."""
+    devs = [torch.device(device)] if device is not None else list(_status_words)
+    for d in devs:
+        v = int(status_word(d).item())
+        if v != 0:
+            status_word(d).zero_()
+            raise RuntimeError(f"castle kernels reported status {v} on {d} (1 = a bounded wait ran out)")
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Grow-only scratch buffer per (device, stream)."""
+    key = (torch.device(device), torch.cuda.current_stream(device).cuda_stream)
+    w = _workspaces.get(key)
+    if w is None or w.numel() < nbytes:
+        w = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = w
+    return w
+
+
+def _desc(t: torch.Tensor) -> CastleTensor:
+    """(B, H, N, d) tensor or view with a contiguous last dim -> castle_tensor_t."""
+    assert t.dim() == 4 and (t.stride(3) == 1 or t.shape[3] == 1)
+    return CastleTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def _aligned_view(t: torch.Tensor) -> torch.Tensor:
+    """Views into the packed projection are used as they are when the ABI's
+    alignment rules hold (16-byte base and strides); otherwise copy."""
+    es = t.element_size()
+    ok = t.stride(3) == 1 and t.data_ptr() % 16 == 0 and all((t.stride(i) * es) % 16 == 0 for i in range(3))
+    return t if ok else t.contiguous()
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+# bounded scratch per launch: the forward's soft-max partials grow with N^2/128 per (batch, head)
+MAX_WORKSPACE_BYTES = 8 << 30
+
+
+class _CastleAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U):
+        _require_cuda(qc, "castle_attention")
+        lib = _lib.load()
+        B, H, N, d = qc.shape
+        orig_dtype = qc.dtype
+        # compute dtype: 16-bit inputs run as they are; fp32 callers run with fp16 operands
+        # (the reference operator does the same: lookahead_keys_attention_triton.py:437-442)
+        cdtype = orig_dtype if orig_dtype in (torch.bfloat16, torch.float16) else torch.float16
+        dp = 64 if d <= 64 else 128
+        if d > 128 or d % 8:
+            raise RuntimeError(f"castle_attention: dim_head {d} not supported (multiples of 8 up to 128)")
+
+        def prep(t):
+            if t.dtype != cdtype:
+                t = t.to(cdtype)
+            if dp != d:
+                t = F.pad(t, (0, dp - d))  # zero columns change no dot product; scale uses the true d
+            return _aligned_view(t)
+
+        ins = [prep(t) for t in (qc, kc, vc, qu, ku, vu)]
+        dev = qc.device
+        need_grad = any(t.requires_grad for t in (qc, kc, vc, qu, ku, vu)) and torch.is_grad_enabled()
+        # laid out (B, N, H, d): merging heads afterwards is a free reshape
+        out = torch.empty(B, N, H, dp, dtype=cdtype, device=dev).permute(0, 2, 1, 3)
+        lse = torch.empty(B, H, N, dtype=torch.float32, device=dev)
+        U = torch.empty(B, H, N, dp, dtype=orig_dtype, device=dev) if return_U else None
+        wst = torch.empty(B, H, N, dp, dtype=torch.float32, device=dev) if need_grad else None
+        st = status_word(dev)
+        # chunk over batch so the partial-softmax scratch stays bounded
+        prob1 = CastleProblem(1, H, N, dp, _DTYPES[cdtype], float(scale))
+        per_b = max(int(lib.castle_fwd_workspace_bytes(ctypes.byref(prob1))), 1)
+        bchunk = max(1, min(B, MAX_WORKSPACE_BYTES // per_b))
+        ws = _workspace(dev, per_b * bchunk)
+        for b0 in range(0, B, bchunk):
+            b1 = min(B, b0 + bchunk)
+            prob = CastleProblem(b1 - b0, H, N, dp, _DTYPES[cdtype], float(scale))
+            d6 = [_desc(t[b0:b1]) for t in ins]
+            do = _desc(out[b0:b1])
+            du = _desc(U[b0:b1]) if return_U else None
+            rc = lib.castle_fwd(ctypes.byref(prob), *[ctypes.byref(x) for x in d6], ctypes.byref(do),
+                                lse[b0:b1].data_ptr(), ctypes.byref(du) if return_U else None,
+                                _DTYPES[orig_dtype], wst[b0:b1].data_ptr() if need_grad else None,
+                                ws.data_ptr(), ws.numel(), st.data_ptr(), _stream(dev))
+            _lib.check(rc, "castle_fwd")
+        if need_grad:
+            ctx.save_for_backward(*ins, out, lse, wst)
+        ctx.scale, ctx.d, ctx.dp, ctx.orig_dtype, ctx.cdtype = float(scale), d, dp, orig_dtype, cdtype
+        o = out[..., :d]
+        if orig_dtype != cdtype:
+            o = o.to(orig_dtype)
+        if return_U:
+            ctx.mark_non_differentiable(U)
+            return o, U[..., :d]
+        return o
+
+    @staticmethod
+    def backward(ctx, do, dU=None):
+        lib = _lib.load()
+        qc, kc, vc, qu, ku, vu, out, lse, wst = ctx.saved_tensors
+        B, H, N, dp = qc.shape
+        d, cdtype, dev = ctx.d, ctx.cdtype, qc.device
+        do = do.to(cdtype)
+        if dp != d:
+            do = F.pad(do, (0, dp - d))
+        do = _aligned_view(do)
+        # the six gradients in the packed layout the projection's backward consumes:
+        # (B, N, 6, H, d) with order qu,ku,vu,qc,kc,vc, handed to the kernels as strided views
+        packed = torch.empty(B, N, 6, H, dp, dtype=cdtype, device=dev)
+        gqu, gku, gvu, gqc, gkc, gvc = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(6))
+        st = status_word(dev)
+        prob = CastleProblem(B, H, N, dp, _DTYPES[cdtype], ctx.scale)
+        nbytes = int(lib.castle_bwd_workspace_bytes(ctypes.byref(prob)))
+        ws = _workspace(dev, nbytes)
+        args = [_desc(t) for t in (qc, kc, vc, qu, ku, vu, out, do)]
+        grads = [_desc(t) for t in (gqc, gkc, gvc, gqu, gku, gvu)]
+        rc = lib.castle_bwd(ctypes.byref(prob), *[ctypes.byref(x) for x in args], lse.data_ptr(), wst.data_ptr(),
+                            *[ctypes.byref(x) for x in grads], ws.data_ptr(), ws.numel(), st.data_ptr(), _stream(dev))
+        _lib.check(rc, "castle_bwd")
+        res = [g[..., :d] for g in (gqc, gkc, gvc, gqu, gku, gvu)]
+        if ctx.orig_dtype != cdtype:
+            res = [g.to(ctx.orig_dtype) for g in res]
+        return (*res, None, None)
+
+
+def castle_attention(qc, kc, vc, qu, ku, vu, scale, return_U_for_cache=False):
+    """Parallel CASTLE attention on (B, H, N, d) tensors (views are fine).
+    Returns `out`, or `(out, U)` when `return_U_for_cache`."""
+    return _CastleAttention.apply(qc, kc, vc, qu, ku, vu, scale, bool(return_U_for_cache))
+
+
+def castle_decode_step(qc, kc, vc, qu, ku, vu, U, qu_cache, kc_cache, vc_cache, cache_len: int, scale: float):
+    """One cached token.  The four caches are (B, H, capacity, d) buffers with `cache_len`
+    valid rows; they are updated IN PLACE (row `cache_len` appended, U[0:cache_len] rewritten).
+    The six new-token tensors are (B, H, 1, d).  Returns out (B, H, 1, d)."""
+    _require_cuda(qc, "castle_decode_step")
+    lib = _lib.load()
+    B, H, one, d = qc.shape
+    assert one == 1
+    dt = qc.dtype
+    if dt not in _DTYPES:
+        raise RuntimeError(f"castle_decode_step: dtype {dt} not supported")
+    cap = U.shape[2]
+    for c in (U, qu_cache, kc_cache, vc_cache):
+        assert c.dtype == dt and c.shape == (B, H, cap, d) and c.stride(3) == 1
+    dev = qc.device
+    news = [_aligned_view(t) for t in (qc, kc, vc, qu, ku, vu)]
+    out = torch.empty(B, H, 1, d, dtype=dt, device=dev)
+    prob = CastleProblem(B, H, 1, d, _DTYPES[dt], float(scale))
+    nbytes = int(lib.castle_decode_workspace_bytes(ctypes.byref(prob), cache_len))
+    ws = _workspace(dev, nbytes)
+    descs = [_desc(t) for t in (*news, U, qu_cache, kc_cache, vc_cache, out)]
+    rc = lib.castle_decode_step(ctypes.byref(prob), cache_len, cap, *[ctypes.byref(x) for x in descs],
+                                ws.data_ptr(), ws.numel(), status_word(dev).data_ptr(), _stream(dev))
+    _lib.check(rc, "castle_decode_step")
+    return out
