@@ -46,7 +46,10 @@ def test_forward_matches_oracle(B, H, N, d, dtype):
     ro, rU = O.castle_parallel(rqc, rkc, rvc, rqu, rku, rvu, scale, return_U=True)
     atol, rtol = BF16_TOL if dtype == torch.bfloat16 else (3e-3, 3e-3)
     _close(out.float().cpu(), ro, atol, rtol, "out")
-    _close(U.float().cpu(), rU, atol, rtol, "U")
+    # U is an un-normalised sum of up to N gate-weighted rows, so its rounding error scales with
+    # its magnitude: allow a few 16-bit ulps of the largest entry on top of the element-wise rule
+    ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    _close(U.float().cpu(), rU, atol + 2 * ulp * rU.abs().max().item(), rtol, "U")
     out2 = castle_attention(qc, kc, vc, qu, ku, vu, scale, False)
     assert torch.equal(out2, out)
 
@@ -61,7 +64,8 @@ def test_forward_matches_reference_golden(name):
     out, U = castle_attention(qc, kc, vc, qu, ku, vu, d ** -0.5, True)
     merged = out.permute(0, 2, 1, 3).reshape(b, n, h * d).float().cpu()
     _close(merged, torch.from_numpy(g["out"]), 3e-3, 3e-3, "out vs reference")
-    _close(U.float().cpu(), torch.from_numpy(g["U"]), 3e-3, 3e-3, "U vs reference")
+    gU = torch.from_numpy(g["U"])
+    _close(U.float().cpu(), gU, 3e-3 + 2 * 2.0 ** -11 * gU.abs().max().item(), 3e-3, "U vs reference")
 
 
 def test_forward_fp32_caller_atol_1e3():
