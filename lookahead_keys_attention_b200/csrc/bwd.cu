@@ -1,10 +1,544 @@
+// CASTLE parallel backward for sm_100a (dim_head 64).
+//
+// One CTA owns a block K of 128 keys and walks the query blocks I from the last
+// one DOWN to K, recomputing the scores flash-style.  Two 128 x d fp32 states
+// live in tensor memory for the whole walk:
+//   W_K  the forward's lookahead state.  It starts as the forward's final state
+//        (= U[K], saved unrounded) and block I is peeled off with a negated
+//        product, W_K -= A[K,I] @ Vu[I], so that before the scores of block I
+//        are rebuilt it equals what the forward saw there.
+//   G_K  = sum_{I' > I} dSu[I',K]^T @ Qc[I']: everything later queries
+//        contribute to d(loss)/d(W_K); it yields dA and dvu for block I.
+// dkc, dvc and dqu of the key block accumulate in tensor memory as well and are
+// written once at the end.  The gradients indexed by the query/position block
+// (dqc, dvu, dku) are summed over key blocks with fp32 vector reductions into a
+// workspace that a last kernel scales and casts.  Thread r owns row r of every
+// accumulator; the soft-max statistics (lse, delta) are per-row registers.
+//
+// Shared memory (224 KB) is time-shared: the 128x128 16-bit operands the
+// threads produce (gate A, masked T, P, dS, dSu, dZ, dT) rotate through four
+// 32 KB slots, two of which overlay input tiles that are dead by then.
 #include "common.cuh"
+#include "sm100.cuh"
+
+namespace castle {
+
+constexpr int kBlkB = 128;
+constexpr uint32_t kPanelB = kBlkB * 128;
+
+struct BwdParams {
+  int B, H, N, nblk;
+  float scale;
+  const float* lse;      // [BH][N]
+  const float* w_state;  // [BH][N][D]
+  float* delta;          // [BH][N]
+  float* acc_dqc;        // [BH][N][D] fp32, zeroed
+  float* acc_dvu;
+  float* acc_dku;
+  castle_tensor_t out, dout;
+  castle_tensor_t dqc, dkc, dvc, dqu, dku, dvu;
+  int32_t* status;
+};
+
+__device__ __forceinline__ float sigmoid_b(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// delta[b,h,i] = sum_d out * dout  (lookahead_keys_attention_triton.py:175-214 in the reference)
+template <typename T, int D>
+__global__ void castle_bwd_delta_kernel(const BwdParams p) {
+  constexpr int LPR = D / 8;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / LPR) + threadIdx.x / LPR;
+  const int sub = threadIdx.x % LPR;
+  const int64_t total = (int64_t)p.B * p.H * p.N;
+  float s = 0.f;
+  if (row < total) {
+    int bh = row / p.N, i = row % p.N, b = bh / p.H, h = bh % p.H;
+    const T* po = reinterpret_cast<const T*>(p.out.ptr) + b * p.out.stride_b + h * p.out.stride_h + (int64_t)i * p.out.stride_n + sub * 8;
+    const T* pd = reinterpret_cast<const T*>(p.dout.ptr) + b * p.dout.stride_b + h * p.dout.stride_h + (int64_t)i * p.dout.stride_n + sub * 8;
+    uint4 a = *reinterpret_cast<const uint4*>(po), c = *reinterpret_cast<const uint4*>(pd);
+    const uint32_t* ua = &a.x; const uint32_t* uc = &c.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 x = Elem<T>::unpack2(ua[j]), y = Elem<T>::unpack2(uc[j]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (row < total && sub == 0) p.delta[row] = s;
+}
+
+// fp32 accumulators -> scaled 16-bit gradients in the caller's (strided) tensors
+template <typename T, int D>
+__global__ void castle_bwd_finish_kernel(const BwdParams p) {
+  constexpr int LPR = D / 8;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / LPR) + threadIdx.x / LPR;
+  const int sub = threadIdx.x % LPR;
+  if (row >= (int64_t)p.B * p.H * p.N) return;
+  int bh = row / p.N, i = row % p.N, b = bh / p.H, h = bh % p.H;
+  const float* srcs[3] = {p.acc_dqc, p.acc_dvu, p.acc_dku};
+  const castle_tensor_t* dsts[3] = {&p.dqc, &p.dvu, &p.dku};
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    const float4* s4 = reinterpret_cast<const float4*>(srcs[t] + row * D + sub * 8);
+    float4 x = s4[0], y = s4[1];
+    uint4 q;
+    q.x = Elem<T>::pack2(x.x * p.scale, x.y * p.scale); q.y = Elem<T>::pack2(x.z * p.scale, x.w * p.scale);
+    q.z = Elem<T>::pack2(y.x * p.scale, y.y * p.scale); q.w = Elem<T>::pack2(y.z * p.scale, y.w * p.scale);
+    T* d = reinterpret_cast<T*>(dsts[t]->ptr) + b * dsts[t]->stride_b + h * dsts[t]->stride_h + (int64_t)i * dsts[t]->stride_n + sub * 8;
+    *reinterpret_cast<uint4*>(d) = q;
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128, 1)
+castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
+                  const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
+                  const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu,
+                  const __grid_constant__ CUtensorMap m_do) {
+  static_assert(D == 64, "this kernel is laid out for dim_head 64");
+  constexpr uint32_t OPB = kPanelB;          // one d-wide operand tile (16 KB)
+  constexpr uint32_t SQB = 2 * kPanelB;      // one 128x128 tile (32 KB)
+  constexpr int FMT = Elem<T>::fmt;
+  constexpr uint32_t ID_SQ_KK = make_idesc(128, 128, FMT, false, false, false);
+  constexpr uint32_t ID_SQ_KM = make_idesc(128, 128, FMT, false, true, false);
+  constexpr uint32_t ID_SQ_MM = make_idesc(128, 128, FMT, true, true, false);
+  constexpr uint32_t ID_D_KM = make_idesc(128, D, FMT, false, true, false);
+  constexpr uint32_t ID_D_KM_NEG = make_idesc(128, D, FMT, false, true, true);
+  constexpr uint32_t ID_D_MM = make_idesc(128, D, FMT, true, true, false);
+  // tensor-memory columns
+  constexpr uint32_t C_W = 0, C_G = 64, C_DKC = 128, C_DVC = 192, C_DQU = 256, C_S = 320, C_X = 448;
+  constexpr uint32_t C_X2 = C_S, C_X3 = C_S + 64;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQu = smem;                 // resident
+  uint8_t* sKc = sQu + OPB;            // resident
+  uint8_t* sQc = sKc + OPB;            // per step
+  uint8_t* sVu = sQc + OPB;            // per step
+  uint8_t* sVD = sVu + OPB;            // [Vc | dO] per step, later slot 3: dS -> dSu -> dT
+  uint8_t* sVc = sVD;
+  uint8_t* sdO = sVD + OPB;
+  uint8_t* sKP = sVD + SQB;            // [Ku | spare], later slot 4: P, then Ku again in the first half
+  uint8_t* sWb = sKP + SQB;
+  uint8_t* sGb = sWb + OPB;
+  uint8_t* sA = sGb + OPB;             // slot 1: gate A
+  uint8_t* sT = sA + SQB;              // slot 2: masked T, later dZ
+  __shared__ uint64_t bar_res, bar_load, bar_ku, bar_mma;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int bh = blockIdx.x, K = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int k0 = K * kBlkB, krow = k0 + tid;
+
+  if (tid == 0) {
+    mbar_init(&bar_res, 1); mbar_init(&bar_load, 1); mbar_init(&bar_ku, 1); mbar_init(&bar_mma, 1);
+    mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+  volatile int* abortp = &abort_flag;
+
+  if (tid == 0) {
+    mbar_expect_tx(&bar_res, 2 * OPB);
+    tma_load_4d(sQu, &m_qu, &bar_res, 0, k0, h, b);
+    tma_load_4d(sKc, &m_kc, &bar_res, 0, k0, h, b);
+  }
+  // W_K starts as the forward's final state
+  {
+    const float* src = p.w_state + ((int64_t)bh * p.N + krow) * D;
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 q = (krow < p.N) ? *reinterpret_cast<const float4*>(src + c * 32 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
+      }
+      tmem_st32(trow + C_W + c * 32, v);
+    }
+    tmem_st_wait();
+  }
+  mbar_wait(&bar_res, 0, abortp);
+  tc_fence_before();
+  __syncthreads();
+
+  uint32_t ph_load = 0, ph_ku = 0, ph_mma = 0;
+  const uint32_t aQu = smem_u32(sQu), aKc = smem_u32(sKc), aQc = smem_u32(sQc), aVu = smem_u32(sVu),
+                 aVc = smem_u32(sVc), adO = smem_u32(sdO), aKP = smem_u32(sKP), aVD = smem_u32(sVD),
+                 aWb = smem_u32(sWb), aGb = smem_u32(sGb), aA = smem_u32(sA), aT = smem_u32(sT);
+  const float inv_scale = 1.f / p.scale;
+
+#define MMA_WAIT()                       \
+  mbar_wait(&bar_mma, ph_mma, abortp);   \
+  ph_mma ^= 1;                           \
+  tc_fence_after();
+#define SMEM_TO_MMA_SYNC() \
+  fence_async_smem();      \
+  tc_fence_before();       \
+  __syncthreads();
+
+  for (int I = p.nblk - 1; I >= K; --I) {
+    const int i0 = I * kBlkB, irow = i0 + tid;
+    const bool diag = (I == K), first = (I == p.nblk - 1);
+    const bool rvalid = irow < p.N;
+    if (tid == 0) {
+      mbar_expect_tx(&bar_load, 5 * OPB);
+      tma_load_4d(sQc, &m_qc, &bar_load, 0, i0, h, b);
+      tma_load_4d(sVu, &m_vu, &bar_load, 0, i0, h, b);
+      tma_load_4d(sVc, &m_vc, &bar_load, 0, k0, h, b);
+      tma_load_4d(sdO, &m_do, &bar_load, 0, i0, h, b);
+      tma_load_4d(sKP, &m_ku, &bar_load, 0, i0, h, b);
+    }
+    const float lse_i = rvalid ? p.lse[(int64_t)bh * p.N + irow] : 0.f;
+    const float delta_i = rvalid ? p.delta[(int64_t)bh * p.N + irow] : 0.f;
+    mbar_wait(&bar_load, ph_load, abortp);
+    ph_load ^= 1;
+
+    // ---- M1: Z = Qu[K] @ Ku[I]^T
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_kk(tmem + C_S, aQu, kPanelB, aKP, kPanelB, 1, ID_SQ_KK, false);
+      mma_commit(&bar_mma);
+    }
+    MMA_WAIT();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {  // gate A (rows k, columns j), zero unless j > k
+      float v[32];
+      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float a = sigmoid_b(v[j] * p.scale);
+        v[j] = (!diag || (i0 + c * 32 + j > krow)) ? a : 0.f;
+      }
+      store_row32<T>(sA, kPanelB, tid, c * 32, v);
+    }
+    SMEM_TO_MMA_SYNC();
+
+    // ---- M2: peel W_K -= A @ Vu[I];  T = Qc[I] @ Vu[I]^T
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_km(tmem + C_W, aA, kPanelB, aVu, kPanelB, 8, ID_D_KM_NEG, true);
+      gemm_kk(tmem + C_S, aQc, kPanelB, aVu, kPanelB, 1, ID_SQ_KK, false);
+      mma_commit(&bar_mma);
+    }
+    MMA_WAIT();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {  // masked T (rows i, columns j <= i), unscaled
+      float v[32];
+      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j <= tid) ? v[j] : 0.f;
+      store_row32<T>(sT, kPanelB, tid, c * 32, v);
+    }
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {  // 16-bit copy of the peeled state
+      float v[32];
+      tmem_ld32(trow + C_W + c * 32, v);
+      tmem_ld_wait();
+      store_row32<T>(sWb, kPanelB, tid, c * 32, v);
+    }
+    SMEM_TO_MMA_SYNC();
+
+    // ---- M3: Su/scale = Qc[I] @ Wb^T + Tm @ A^T
+    if (tid == 0) {
+      tc_fence_after();
+      if (!diag) gemm_kk(tmem + C_S, aQc, kPanelB, aWb, kPanelB, 1, ID_SQ_KK, false);
+      gemm_kk(tmem + C_S, aT, kPanelB, aA, kPanelB, 2, ID_SQ_KK, !diag);
+      mma_commit(&bar_mma);
+    }
+    MMA_WAIT();
+    uint32_t dpk[64];  // silu'(Su), later dSu, two 16-bit values per register
+    uint32_t ppk[64];  // P
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float v[32];
+      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float su0 = v[j] * p.scale, su1 = v[j + 1] * p.scale;
+        float g0 = sigmoid_b(su0), g1 = sigmoid_b(su1);
+        v[j] = -su0 * g0 * inv_scale;
+        v[j + 1] = -su1 * g1 * inv_scale;
+        dpk[c * 16 + j / 2] = Elem<T>::pack2(g0 * (1.f + su0 * (1.f - g0)), g1 * (1.f + su1 * (1.f - g1)));
+      }
+      tmem_st32(trow + C_S + c * 32, v);
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- M4: S/scale = penalty + Qc[I] @ Kc[K]^T
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_kk(tmem + C_S, aQc, kPanelB, aKc, kPanelB, 1, ID_SQ_KK, true);
+      mma_commit(&bar_mma);
+    }
+    MMA_WAIT();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // P = exp(S - lse) (rows i, columns k); into slot 4 over Ku
+      float v[32];
+      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        bool ok0 = rvalid && (!diag || (c * 32 + j <= tid)), ok1 = rvalid && (!diag || (c * 32 + j + 1 <= tid));
+        v[j] = ok0 ? __expf(v[j] * p.scale - lse_i) : 0.f;
+        v[j + 1] = ok1 ? __expf(v[j + 1] * p.scale - lse_i) : 0.f;
+        ppk[c * 16 + j / 2] = Elem<T>::pack2(v[j], v[j + 1]);
+      }
+      store_row32<T>(sKP, kPanelB, tid, c * 32, v);
+    }
+    SMEM_TO_MMA_SYNC();
+
+    // ---- M5: dvc += P^T @ dO[I];  dP = dO[I] @ Vc[K]^T
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_mm(tmem + C_DVC, aKP, kPanelB, adO, kPanelB, 8, ID_D_MM, !first);
+      gemm_kk(tmem + C_S, adO, kPanelB, aVc, kPanelB, 1, ID_SQ_KK, false);
+      mma_commit(&bar_mma);
+    }
+    MMA_WAIT();
+    if (tid == 0) {  // P is consumed: bring Ku[I] back for the dqu product
+      mbar_expect_tx(&bar_ku, OPB);
+      tma_load_4d(sKP, &m_ku, &bar_ku, 0, i0, h, b);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // dS = P * (dP - delta) -> slot 3 (over Vc|dO); dSu = -dS * silu'(Su) stays in registers
+      float v[32];
+      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float2 pp = Elem<T>::unpack2(ppk[c * 16 + j / 2]);
+        float2 dd = Elem<T>::unpack2(dpk[c * 16 + j / 2]);
+        float ds0 = pp.x * (v[j] - delta_i), ds1 = pp.y * (v[j + 1] - delta_i);
+        v[j] = ds0; v[j + 1] = ds1;
+        dpk[c * 16 + j / 2] = Elem<T>::pack2(-ds0 * dd.x, -ds1 * dd.y);
+      }
+      store_row32<T>(sVD, kPanelB, tid, c * 32, v);
+    }
+    SMEM_TO_MMA_SYNC();
+
+    // ---- M6: dkc += dS^T @ Qc[I];  X = dS @ Kc[K]
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_mm(tmem + C_DKC, aVD, kPanelB, aQc, kPanelB, 8, ID_D_MM, !first);
+      gemm_km(tmem + C_X, aVD, kPanelB, aKc, kPanelB, 8, ID_D_KM, false);
+      mma_commit(&bar_mma);
+    }
+    MMA_WAIT();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // dSu -> slot 3
+      uint8_t* panel = sVD + (c >> 1) * kPanelB;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 w = make_uint4(dpk[c * 16 + q * 4], dpk[c * 16 + q * 4 + 1], dpk[c * 16 + q * 4 + 2], dpk[c * 16 + q * 4 + 3]);
+        *reinterpret_cast<uint4*>(panel + swz_off(tid, (c & 1) * 4 + q)) = w;
+      }
+    }
+    SMEM_TO_MMA_SYNC();
+
+    // ---- M7: X += dSu @ Wb;  dA/scale = Gb @ Vu[I]^T + dSu^T @ Tm   (rows k, columns j)
+    if (tid == 0) {
+      tc_fence_after();
+      if (!diag) gemm_km(tmem + C_X, aVD, kPanelB, aWb, kPanelB, 8, ID_D_KM, true);
+      if (!first) gemm_kk(tmem + C_S, aGb, kPanelB, aVu, kPanelB, 1, ID_SQ_KK, false);
+      gemm_mm(tmem + C_S, aVD, kPanelB, aT, kPanelB, 8, ID_SQ_MM, !first);
+      mma_commit(&bar_mma);
+    }
+    MMA_WAIT();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {  // dZ = dA * A * (1 - A) -> slot 2 (over Tm)
+      float v[32], a[32];
+      tmem_ld32(trow + C_S + c * 32, v);
+      load_row32<T>(sA, kPanelB, tid, c * 32, a);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = v[j] * p.scale * a[j] * (1.f - a[j]);
+      store_row32<T>(sT, kPanelB, tid, c * 32, v);
+    }
+    SMEM_TO_MMA_SYNC();
+
+    // ---- M8: G += dSu^T @ Qc[I];  dT = dSu @ A;  dqu += dZ @ Ku[I]
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_mm(tmem + C_G, aVD, kPanelB, aQc, kPanelB, 8, ID_D_MM, !first);
+      gemm_km(tmem + C_S, aVD, kPanelB, aA, kPanelB, 8, ID_SQ_KM, false);
+      mbar_wait(&bar_ku, ph_ku, abortp);
+      gemm_km(tmem + C_DQU, aT, kPanelB, aKP, kPanelB, 8, ID_D_KM, !first);
+      mma_commit(&bar_mma);
+    }
+    ph_ku ^= 1;
+    MMA_WAIT();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {  // masked dT (rows i, columns j <= i) -> slot 3 (over dSu)
+      float v[32];
+      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j <= tid) ? v[j] : 0.f;
+      store_row32<T>(sVD, kPanelB, tid, c * 32, v);
+    }
+    SMEM_TO_MMA_SYNC();
+
+    // ---- M9: X += dT @ Vu[I];  X2 = A^T @ Gb + dT^T @ Qc[I];  X3 = dZ^T @ Qu[K]
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_km(tmem + C_X, aVD, kPanelB, aVu, kPanelB, 8, ID_D_KM, true);
+      if (!first) gemm_mm(tmem + C_X2, aA, kPanelB, aGb, kPanelB, 8, ID_D_MM, false);
+      gemm_mm(tmem + C_X2, aVD, kPanelB, aQc, kPanelB, 8, ID_D_MM, !first);
+      gemm_mm(tmem + C_X3, aT, kPanelB, aQu, kPanelB, 8, ID_D_MM, false);
+      mma_commit(&bar_mma);
+    }
+    MMA_WAIT();
+    {
+      const int64_t rbase = ((int64_t)bh * p.N + irow) * D;
+      const uint32_t cols[3] = {C_X, C_X2, C_X3};
+      float* dsts[3] = {p.acc_dqc, p.acc_dvu, p.acc_dku};
+#pragma unroll
+      for (int t = 0; t < 3; ++t) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          float v[32];
+          tmem_ld32(trow + cols[t] + c * 32, v);
+          tmem_ld_wait();
+          if (rvalid) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) red_add_v4(dsts[t] + rbase + c * 32 + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+          }
+        }
+      }
+    }
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {  // 16-bit copy of G including block I, for the next (lower) block
+      float v[32];
+      tmem_ld32(trow + C_G + c * 32, v);
+      tmem_ld_wait();
+      store_row32<T>(sGb, kPanelB, tid, c * 32, v);
+    }
+    SMEM_TO_MMA_SYNC();
+  }
+#undef MMA_WAIT
+#undef SMEM_TO_MMA_SYNC
+
+  // ---- key-block gradients: dkc (x scale), dvc, dqu (x scale)
+  {
+    tc_fence_after();
+    const uint32_t cols[3] = {C_DKC, C_DVC, C_DQU};
+    const castle_tensor_t* dsts[3] = {&p.dkc, &p.dvc, &p.dqu};
+    const float mul[3] = {p.scale, 1.f, p.scale};
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+      T* dst = reinterpret_cast<T*>(dsts[t]->ptr) + b * dsts[t]->stride_b + h * dsts[t]->stride_h + (int64_t)krow * dsts[t]->stride_n;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        float v[32];
+        tmem_ld32(trow + cols[t] + c * 32, v);
+        tmem_ld_wait();
+        if (krow < p.N) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 q;
+            q.x = Elem<T>::pack2(v[8 * j] * mul[t], v[8 * j + 1] * mul[t]);
+            q.y = Elem<T>::pack2(v[8 * j + 2] * mul[t], v[8 * j + 3] * mul[t]);
+            q.z = Elem<T>::pack2(v[8 * j + 4] * mul[t], v[8 * j + 5] * mul[t]);
+            q.w = Elem<T>::pack2(v[8 * j + 6] * mul[t], v[8 * j + 7] * mul[t]);
+            *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = q;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+  if (tid == 0 && abort_flag) atomicOr(p.status, CASTLE_STATUS_WAIT_TIMEOUT);
+}
+
+template <typename T, int D>
+static int launch_bwd(const BwdParams& p, const CUtensorMap* maps, cudaStream_t st) {
+  constexpr size_t smem = 7 * kPanelB + 4 * 2 * kPanelB - kPanelB + 1024;  // 224 KB + alignment slack
+  {  // per device, so set on every call (cheap)
+    cudaError_t e = cudaFuncSetAttribute(castle_bwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e, "castle_bwd attribute");
+  }
+  const int64_t rows = (int64_t)p.B * p.H * p.N;
+  constexpr int RPB = 256 / (D / 8);
+  cudaError_t e = cudaMemsetAsync(p.acc_dqc, 0, (size_t)rows * D * 3 * sizeof(float), st);
+  if (e != cudaSuccess) return cuda_fail(e, "castle_bwd memset");
+  castle_bwd_delta_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
+  dim3 grid(p.B * p.H, p.nblk);
+  castle_bwd_kernel<T, D><<<grid, 128, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6]);
+  castle_bwd_finish_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : cuda_fail(e, "castle_bwd launch");
+}
+
+}  // namespace castle
+
 using namespace castle;
-extern "C" size_t castle_bwd_workspace_bytes(const castle_problem_t*) { return 0; }
-extern "C" int castle_bwd(const castle_problem_t*, const castle_tensor_t*, const castle_tensor_t*, const castle_tensor_t*,
-                          const castle_tensor_t*, const castle_tensor_t*, const castle_tensor_t*, const castle_tensor_t*,
-                          const castle_tensor_t*, const float*, const float*, const castle_tensor_t*,
-                          const castle_tensor_t*, const castle_tensor_t*, const castle_tensor_t*, const castle_tensor_t*,
-                          const castle_tensor_t*, void*, size_t, int32_t*, void*) {
-  return reject("castle_bwd: not built");
+
+extern "C" size_t castle_bwd_workspace_bytes(const castle_problem_t* p) {
+  if (!p || p->seq_len <= 0) return 0;
+  int64_t rows = (int64_t)p->batch * p->heads * p->seq_len;
+  return (size_t)(rows * (3 * p->dim_head + 1) * sizeof(float));
+}
+
+extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
+                          const castle_tensor_t* vc, const castle_tensor_t* qu, const castle_tensor_t* ku,
+                          const castle_tensor_t* vu, const castle_tensor_t* out, const castle_tensor_t* dout,
+                          const float* lse, const float* w_state, const castle_tensor_t* dqc,
+                          const castle_tensor_t* dkc, const castle_tensor_t* dvc, const castle_tensor_t* dqu,
+                          const castle_tensor_t* dku, const castle_tensor_t* dvu, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream) {
+  if (!p) return reject("castle_bwd: null problem");
+  if (p->batch <= 0 || p->heads <= 0 || p->seq_len <= 0) return reject("castle_bwd: empty problem");
+  if (p->dim_head != 64) return reject("castle_bwd: dim_head %d not supported (64)", p->dim_head);
+  if (p->dtype != CASTLE_BF16 && p->dtype != CASTLE_F16) return reject("castle_bwd: dtype %d not supported (bf16, fp16)", p->dtype);
+  int nblk = (p->seq_len + kBlkB - 1) / kBlkB;
+  if (nblk > 65535) return reject("castle_bwd: sequence too long");
+  int rc = 0;
+  const castle_tensor_t* ts[14] = {qc, kc, vc, qu, ku, vu, dout, out, dqc, dkc, dvc, dqu, dku, dvu};
+  const char* names[14] = {"qc", "kc", "vc", "qu", "ku", "vu", "dout", "out", "dqc", "dkc", "dvc", "dqu", "dku", "dvu"};
+  for (int i = 0; i < 14; ++i)
+    if (!tensor_ok(ts[i], p->dtype, names[i], &rc)) return rc;
+  if (!lse || !w_state || !status) return reject("castle_bwd: lse, w_state and status must not be null");
+  size_t need = castle_bwd_workspace_bytes(p);
+  if (!workspace || workspace_bytes < need)
+    return reject("castle_bwd: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
+  if (((uintptr_t)workspace) % 16) return reject("castle_bwd: workspace not 16-byte aligned");
+
+  BwdParams bp;
+  bp.B = p->batch; bp.H = p->heads; bp.N = p->seq_len; bp.nblk = nblk; bp.scale = p->scale;
+  bp.lse = lse; bp.w_state = w_state;
+  int64_t rows = (int64_t)p->batch * p->heads * p->seq_len;
+  bp.acc_dqc = (float*)workspace;
+  bp.acc_dvu = bp.acc_dqc + rows * p->dim_head;
+  bp.acc_dku = bp.acc_dvu + rows * p->dim_head;
+  bp.delta = bp.acc_dku + rows * p->dim_head;
+  bp.out = *out; bp.dout = *dout;
+  bp.dqc = *dqc; bp.dkc = *dkc; bp.dvc = *dvc; bp.dqu = *dqu; bp.dku = *dku; bp.dvu = *dvu;
+  bp.status = status;
+  CUtensorMap maps[7];
+  for (int i = 0; i < 7; ++i) {
+    rc = make_tmap_16bit(&maps[i], ts[i], p->dtype, p->batch, p->heads, p->seq_len, p->dim_head, kBlkB, names[i]);
+    if (rc) return rc;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p->dtype == CASTLE_BF16) return launch_bwd<__nv_bfloat16, 64>(bp, maps, st);
+  return launch_bwd<__half, 64>(bp, maps, st);
 }

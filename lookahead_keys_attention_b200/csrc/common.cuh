@@ -62,6 +62,10 @@ inline int make_tmap_16bit(CUtensorMap* m, const castle_tensor_t* t, int dtype, 
                            int box_rows, const char* name) {
   encode_tiled_fn fn = get_encode_fn();
   if (!fn) return reject("cuTensorMapEncodeTiled is not available from this driver");
+  // The encoder is a driver call and needs a current context on the calling thread; a thread
+  // that has made no runtime call yet (an autograd worker, say) has none until one is made.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { cudaFree(nullptr); ctx_bound = true; }
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
   // a size-1 dimension may carry any stride; give it a legal one
   cuuint64_t sn = (cuuint64_t)t->stride_n * 2, sh = (cuuint64_t)t->stride_h * 2, sb = (cuuint64_t)t->stride_b * 2;

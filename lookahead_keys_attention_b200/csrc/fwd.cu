@@ -368,11 +368,9 @@ __global__ void __launch_bounds__(256) castle_fwd_merge_kernel(const FwdParams p
 template <typename T, int D>
 static int launch_fwd(const FwdParams& p, const CUtensorMap* maps, cudaStream_t st) {
   constexpr size_t smem = 5 * (D / 64) * kPanelBytes + 2 * 2 * kPanelBytes + 1024;
-  static bool attr_done = false;
-  if (!attr_done) {
+  {  // per device, so set on every call (cheap)
     cudaError_t e = cudaFuncSetAttribute(castle_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cuda_fail(e, "castle_fwd attribute");
-    attr_done = true;
   }
   dim3 grid(p.B * p.H, p.nblk);
   castle_fwd_kernel<T, D><<<grid, 128, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);

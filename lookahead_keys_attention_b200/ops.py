@@ -105,7 +105,7 @@ class _CastleAttention(torch.autograd.Function):
 
         ins = [prep(t) for t in (qc, kc, vc, qu, ku, vu)]
         dev = qc.device
-        need_grad = any(t.requires_grad for t in (qc, kc, vc, qu, ku, vu)) and torch.is_grad_enabled()
+        need_grad = any(ctx.needs_input_grad[:6])
         # laid out (B, N, H, d): merging heads afterwards is a free reshape
         out = torch.empty(B, N, H, dp, dtype=cdtype, device=dev).permute(0, 2, 1, 3)
         lse = torch.empty(B, H, N, dtype=torch.float32, device=dev)

@@ -87,3 +87,77 @@ def test_forward_causality():
     full = castle_attention(qc, kc, vc, qu, ku, vu, 0.125, False)
     half = castle_attention(*[t[:, :, :150] for t in (qc, kc, vc, qu, ku, vu)], 0.125, False)
     _close(full[:, :, :150].float(), half.float(), 1e-3, 0.0, "prefix invariance")
+
+
+# q/k/v of a default-initialised projection of x ~ N(0,1) have std 1/sqrt(3): nn.Linear draws
+# its weights uniformly in +-1/sqrt(fan_in).  The tolerance tests use inputs of that scale.
+PROJ_STD = 3 ** -0.5
+
+
+def _grads(B, H, N, d, dtype, seed, std=PROJ_STD, want_ref16=False):
+    from lookahead_keys_attention_b200 import castle_attention, check_status
+    packed = (_inputs(B, H, N, d, torch.float32, seed=seed) * std).to(dtype)
+    torch.manual_seed(seed + 1)
+    gout = torch.randn(B, H, N, d).to(dtype)
+    pk = packed.cuda().requires_grad_()
+    qu, ku, vu, qc, kc, vc = _views(pk)
+    scale = d ** -0.5
+    out = castle_attention(qc, kc, vc, qu, ku, vu, scale, False)
+    out.backward(gout.cuda())
+    torch.cuda.synchronize()
+    check_status()
+    rqu, rku, rvu, rqc, rkc, rvc = [t.float() for t in _views(packed)]
+    ref = O.castle_parallel_bwd(rqc, rkc, rvc, rqu, rku, rvu, scale, gout.float())  # dqc,dkc,dvc,dqu,dku,dvu
+    got = pk.grad.float().cpu()
+    gqu, gku, gvu, gqc, gkc, gvc = _views(got)
+    if want_ref16:  # the reference's own arithmetic in the 16-bit dtype, on the CPU
+        r16 = _views(packed)
+        ref16 = O.castle_parallel_bwd(r16[3], r16[4], r16[5], r16[0], r16[1], r16[2], scale, gout)
+        return [(g, r, r16_.float()) for g, r, r16_ in zip((gqc, gkc, gvc, gqu, gku, gvu), ref, ref16)]
+    return dict(dqc=(gqc, ref[0]), dkc=(gkc, ref[1]), dvc=(gvc, ref[2]), dqu=(gqu, ref[3]), dku=(gku, ref[4]), dvu=(gvu, ref[5]))
+
+
+@pytest.mark.parametrize("B,H,N,d", [(1, 1, 128, 64), (1, 1, 256, 64), (2, 2, 384, 64), (1, 2, 200, 64), (1, 1, 1, 64),
+                                     (1, 1, 129, 64), (1, 2, 40, 16), (1, 1, 77, 32), (1, 1, 1024, 64)])
+def test_backward_matches_oracle_bf16(B, H, N, d):
+    res = _grads(B, H, N, d, torch.bfloat16, seed=N + d)
+    for name, (g, r) in res.items():
+        _close(g, r, *BF16_TOL, name)
+
+
+@pytest.mark.parametrize("B,H,N,d", [(1, 2, 256, 64), (1, 1, 200, 32)])
+def test_backward_matches_oracle_fp16(B, H, N, d):
+    res = _grads(B, H, N, d, torch.float16, seed=N + d)
+    for name, (g, r) in res.items():
+        _close(g, r, 5e-3, 5e-3, name)
+
+
+def test_backward_matches_reference_golden():
+    """Gradients of the reference's own autograd (fp64, recorded) vs the kernels run with fp16 operands."""
+    from lookahead_keys_attention_b200 import castle_attention
+    g = load_golden("core_n200_d64")
+    (b, h, n, d), packed, gout = rebuild_core_case(g)
+    pk = packed.float().cuda().requires_grad_()
+    qu, ku, vu, qc, kc, vc = O.split_heads(pk, h)
+    out = castle_attention(qc, kc, vc, qu, ku, vu, d ** -0.5, False)
+    out.backward(gout.float().view(b, n, h, d).permute(0, 2, 1, 3).cuda())
+    _close(pk.grad.cpu(), torch.from_numpy(g["dpacked"]), 2e-2, 0.0, "packed grads vs reference (atol 2e-2)")
+
+
+@pytest.mark.parametrize("N", [256, 1024])
+def test_backward_unit_variance_inputs_no_worse_than_16bit_reference(N):
+    """With N(0,1) q/k/v the lookahead state reaches tens and 16-bit rounding alone breaks the
+    element-wise rule - for the reference's own bf16 run too.  There the bar is the reference's
+    error: the kernel's max error stays within 1.5x of the CPU bf16 run's."""
+    names = ("dqc", "dkc", "dvc", "dqu", "dku", "dvu")
+    for name, (g, r, r16) in zip(names, _grads(1, 1, N, 64, torch.bfloat16, seed=N, std=1.0, want_ref16=True)):
+        e, e16 = (g - r).abs().max().item(), (r16 - r).abs().max().item()
+        assert e <= 1.5 * e16 + 2e-3, f"{name}: kernel {e:.3e} vs reference-bf16 {e16:.3e}"
+
+
+def test_backward_deterministic_forward_state():
+    """Two identical calls give identical key-block gradients (dkc, dvc, dqu are not reduced atomically)."""
+    a = _grads(1, 2, 300, 64, torch.bfloat16, seed=11)
+    b = _grads(1, 2, 300, 64, torch.bfloat16, seed=11)
+    for name in ("dkc", "dvc", "dqu"):
+        assert torch.equal(a[name][0], b[name][0]), name
