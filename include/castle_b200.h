@@ -116,6 +116,15 @@ int castle_decode_step(const castle_problem_t* p, int32_t cache_len, int32_t cap
                        const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache, const castle_tensor_t* out,
                        void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* ---- measurement aid ------------------------------------------------------
+ * (no counterpart in the reference)  Bracket the MAIN kernel of later calls (from
+ * any host thread of the process) with two caller-owned CUDA events recorded on the launch
+ * stream: which = 0 forward, 1 backward, 2 decode step.  Pass NULL events to
+ * stop.  Lets a benchmark time the dominant kernel alone, without a profiler.
+ */
+enum { CASTLE_KERNEL_FWD = 0, CASTLE_KERNEL_BWD = 1, CASTLE_KERNEL_DECODE = 2 };
+int castle_set_kernel_events(int32_t which, void* start_event, void* stop_event);
+
 /* ---- self test -------------------------------------------------------------
  * Runs one 128x128 tensor-core product through each operand form the kernels
  * use (no counterpart in the reference).  `x`, `y`: bf16 [128][128] device

@@ -482,7 +482,9 @@ static int launch_bwd(const BwdParams& p, const CUtensorMap* maps, cudaStream_t 
   if (e != cudaSuccess) return cuda_fail(e, "castle_bwd memset");
   castle_bwd_delta_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
   dim3 grid(p.B * p.H, p.nblk);
+  ev_start(CASTLE_KERNEL_BWD, st);
   castle_bwd_kernel<T, D><<<grid, 128, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6]);
+  ev_stop(CASTLE_KERNEL_BWD, st);
   castle_bwd_finish_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : cuda_fail(e, "castle_bwd launch");

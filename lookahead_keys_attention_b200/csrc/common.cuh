@@ -14,6 +14,11 @@ namespace castle {
 
 char* last_error_buf();  // thread-local, defined in api.cu
 
+struct KernelEvents { cudaEvent_t start = nullptr, stop = nullptr; };
+KernelEvents& kernel_events(int which);  // process-wide, defined in api.cu
+inline void ev_start(int which, cudaStream_t st) { auto& e = kernel_events(which); if (e.start) cudaEventRecord(e.start, st); }
+inline void ev_stop(int which, cudaStream_t st) { auto& e = kernel_events(which); if (e.stop) cudaEventRecord(e.stop, st); }
+
 inline int reject(const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);

@@ -251,7 +251,9 @@ static int decode_nsplit(int BH, int t) {
 template <typename T, int D>
 static int launch_decode(const DecodeParams& p, int BH, cudaStream_t st) {
   dim3 grid(BH, p.nsplit);
+  ev_start(CASTLE_KERNEL_DECODE, st);
   castle_decode_kernel<T, D><<<grid, kDecodeThreads, 0, st>>>(p);
+  ev_stop(CASTLE_KERNEL_DECODE, st);
   if (p.nsplit > 1) castle_decode_merge_kernel<T, D><<<BH, D, 0, st>>>(p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : cuda_fail(e, "castle_decode_step launch");

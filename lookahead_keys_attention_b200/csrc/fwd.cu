@@ -373,7 +373,9 @@ static int launch_fwd(const FwdParams& p, const CUtensorMap* maps, cudaStream_t 
     if (e != cudaSuccess) return cuda_fail(e, "castle_fwd attribute");
   }
   dim3 grid(p.B * p.H, p.nblk);
+  ev_start(CASTLE_KERNEL_FWD, st);
   castle_fwd_kernel<T, D><<<grid, 128, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+  ev_stop(CASTLE_KERNEL_FWD, st);
   constexpr int ROWS = 256 / (D / 4);
   dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);
   castle_fwd_merge_kernel<T, D><<<g2, 256, 0, st>>>(p);

@@ -1,0 +1,118 @@
+"""GPU: the `Castle` module against the golden vectors recorded from the reference module and
+against the oracle - the five properties the reference's own tests check
+(tests/test_lookahead.py in the reference: parallel == sequential :10-64, kernel == PyTorch path
+forward and all gradients :67-143, causality :145-222, prefill-with-U then decode :225-282)."""
+import pytest
+import torch
+
+from conftest import load_golden, rebuild_module_case
+from oracle import castle_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+MODULE_CASES = ["module_d16", "module_d16_prenorm", "module_d32", "module_d64_n256", "module_readme"]
+
+
+def _build(cfg, w1, w2, nw, dtype=torch.float32):
+    from lookahead_keys_attention_b200 import Castle
+    m = Castle(cfg["dim"], heads=cfg["heads"], dim_head=cfg["dim_head"], prenorm=cfg["prenorm"]).cuda()
+    sd = {"to_all_qkv.weight": w1, "combine_heads.weight": w2}
+    if nw is not None:
+        sd["norm.weight"] = nw
+    m.load_state_dict(sd)  # same keys as the reference module
+    return m.to(dtype)
+
+
+@pytest.mark.parametrize("name", MODULE_CASES)
+def test_module_fp32_forward_and_grads_vs_reference(name):
+    """fp32 module: forward atol 1e-3, input and parameter gradients atol 2e-2
+    (the reference's tolerances, tests/test_lookahead.py:114,135,143)."""
+    g = load_golden(name)
+    cfg, w1, w2, nw, x, gout = rebuild_module_case(g)
+    st = cfg["stride"]
+    m = _build(cfg, w1, w2, nw)
+    xg = x.cuda().requires_grad_()
+    out = m(xg)
+    out.backward(gout.cuda())
+    assert torch.allclose(out.detach().cpu()[:, ::st], torch.from_numpy(g["out"]), atol=1e-3)
+    assert torch.allclose(xg.grad.cpu()[:, ::st], torch.from_numpy(g["dx"]), atol=2e-2)
+    assert torch.allclose(m.to_all_qkv.weight.grad.cpu()[::37, ::11], torch.from_numpy(g["dw_qkv_sample"]), atol=2e-2)
+    assert torch.allclose(m.combine_heads.weight.grad.cpu()[::11, ::13], torch.from_numpy(g["dw_out_sample"]), atol=2e-2)
+
+
+@pytest.mark.parametrize("name", MODULE_CASES)
+@torch.no_grad()
+def test_module_prefill_then_decode_vs_reference(name):
+    """Prefill (kernel emits U) + cached single-token steps == the reference's sequential outputs, atol 1e-3."""
+    from lookahead_keys_attention_b200 import check_status
+    g = load_golden(name)
+    cfg, w1, w2, nw, x, _ = rebuild_module_case(g)
+    st, split, n = cfg["stride"], cfg["split"], cfg["n"]
+    m = _build(cfg, w1, w2, nw)
+    xc = x.cuda()
+    pre, cache = m(xc[:, :split], return_next_cache=True)
+    assert cache.U.shape == (cfg["b"], cfg["heads"], split, cfg["dim_head"])
+    gU = torch.from_numpy(g["prefill_U"])
+    assert torch.allclose(cache.U.cpu(), gU, atol=1e-3 + 2 * 2.0 ** -11 * gU.abs().max().item())
+    outs = [pre]
+    for t in range(split, n):
+        o, cache = m(xc[:, t:t + 1], cache=cache)  # return_next_cache defaults to True for one token
+        assert cache.kc_cache.shape[-2] == t + 1
+        outs.append(o)
+    seq = torch.cat(outs, 1).cpu()
+    check_status()
+    assert torch.allclose(seq[:, ::st], torch.from_numpy(g["seq_out"]), atol=1e-3)
+    assert torch.allclose(cache.qu_cache.cpu()[:, :, ::st], torch.from_numpy(g["final_qu"]), atol=1e-3)
+    # parallel == sequential (README contract, atol 1e-3)
+    assert torch.allclose(seq, m(xc).cpu(), atol=1e-3)
+
+
+@torch.no_grad()
+def test_module_decode_from_empty_cache_and_functional_mode():
+    from lookahead_keys_attention_b200 import Castle
+    torch.manual_seed(0)
+    m = Castle(64, heads=2, dim_head=32, inplace_cache=False).cuda()
+    x = torch.randn(2, 6, 64, device="cuda")
+    cache, outs, caches = None, [], []
+    for t in range(6):
+        o, cache = m(x[:, t:t + 1], cache=cache)
+        outs.append(o)
+        caches.append(cache)
+    assert torch.allclose(torch.cat(outs, 1), m(x), atol=1e-3)
+    # functional mode: an old cache is still what it was, and stepping from it again gives the same answer
+    o_again, _ = m(x[:, 3:4], cache=caches[2])
+    assert torch.allclose(o_again, outs[3], atol=1e-6)
+
+
+@torch.no_grad()
+def test_module_causality_bf16():
+    from lookahead_keys_attention_b200 import Castle
+    torch.manual_seed(1)
+    m = Castle(128, heads=2, dim_head=64, prenorm=True).cuda().bfloat16()
+    x = torch.randn(2, 64, 128, device="cuda").bfloat16()
+    assert torch.allclose(m(x)[:, :32].float(), m(x[:, :32]).float(), atol=1e-3)
+
+
+def test_module_bf16_vs_fp32_oracle():
+    """bf16 module at a few hundred tokens: |a-b| <= 2e-2 + 1e-2|b| against the fp32 oracle on the
+    same bf16-rounded weights and inputs, for the output, dx and both weight gradients."""
+    from lookahead_keys_attention_b200 import Castle
+    torch.manual_seed(2)
+    m = Castle(256, heads=4, dim_head=64).cuda().bfloat16()
+    x = torch.randn(2, 512, 256).bfloat16()
+    gout = torch.randn(2, 512, 256).bfloat16()
+    xg = x.cuda().requires_grad_()
+    out = m(xg)
+    out.backward(gout.cuda())
+    w1 = m.to_all_qkv.weight.detach().float().cpu().requires_grad_()
+    w2 = m.combine_heads.weight.detach().float().cpu().requires_grad_()
+    xr = x.float().requires_grad_()
+    ref = O.castle_module_forward(xr, w1, w2, 4, 64)
+    ref.backward(gout.float())
+    for what, a, b in [("out", out, ref.detach()), ("dx", xg.grad, xr.grad)]:
+        err = (a.float().cpu() - b).abs()
+        assert bool((err <= 2e-2 + 1e-2 * b.abs()).all()), f"{what}: {err.max().item():.3e}"
+    # weight gradients sum over 1024 tokens: compare relative to their scale (rel-Frobenius 1e-2)
+    for what, a, b in [("dW_qkv", m.to_all_qkv.weight.grad, w1.grad), ("dW_out", m.combine_heads.weight.grad, w2.grad)]:
+        rel = ((a.float().cpu() - b).norm() / b.norm()).item()
+        assert rel < 1e-2, f"{what}: rel-F {rel:.3e}"
