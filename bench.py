@@ -1,0 +1,421 @@
+#!/usr/bin/env python
+"""Benchmark of the CASTLE hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-decode]
+
+N > 1 is launched by torchrun (one rank per GPU); ranks own disjoint (batch, head)
+rectangles of the workload and never communicate inside the timed path.
+
+Workload (synthetic, seeded): a single CASTLE attention layer in bf16, B=4, N=4096, H=16,
+d_head=64, dim=1024; x ~ N(0,1), default-initialised projections, upstream gradient ~ N(0,1).
+One step = forward + backward of the attention core.
+
+  value     whole-job TFLOP/s of the core (forward + backward kernels, q/k/v already in HBM),
+            counted with the ALGORITHMIC flops 19 * B*H*N^2*d (5 forward + 14 backward incl.
+            recompute); the reference's cubic N^3 term is not credited.
+  e2e       the same flops over the time of `Castle(x)` forward + backward called with HOST
+            tensors: pinned x and upstream grad copied in, out and dx copied back, projections
+            included.
+  roofline  the backward main kernel alone, timed with CUDA events recorded around it.
+  decode    (secondary) cached single-token decode at B=64, H=16, d=128, prefix 8192, 256 steps.
+
+`--impl reference` times the CPU oracle (a restatement of the reference's PyTorch path) on the
+host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CFG = dict(batch=4, seq_len=4096, heads=16, dim_head=64, dim=1024)
+DECODE_CFG = dict(batch=64, prefix=8192, heads=16, dim_head=128, dim=2048, steps=256)
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(tflops=float(d["bf16_tflops"]), hbm=float(d["hbm_gbs"]), source="measured")
+    return dict(tflops=1590.0, hbm=6650.0, source="fallback")
+
+
+def core_flops(b, h, n, d):
+    u = b * h * n * n * d
+    return 5 * u, 14 * u
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+
+    def _open(self):
+        import pynvml as nv
+        nv.nvmlInit()
+        idx = self.index
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            try:
+                idx = int(vis.split(",")[self.index])
+            except ValueError:
+                pass
+        self._nv, self._h = nv, nv.nvmlDeviceGetHandleByIndex(idx)
+        self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self._h, nv.NVML_CLOCK_SM)
+
+    def _run(self):
+        try:
+            nv, h = self._nv, self._h
+            names = {
+                getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+            }
+            while not self._stop.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    for bit, name in names.items():
+                        if r & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+                time.sleep(0.005)
+        except Exception as e:  # NVML missing: report that, do not fail the run
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def __enter__(self):
+        try:
+            self._open()  # NVML start-up takes longer than a short timed region: do it before
+        except Exception as e:
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+            return self
+        self._thr = threading.Thread(target=self._run, daemon=True)
+        self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join(2)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def dist_setup(gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    assert world == gpus, f"--gpus {gpus} but WORLD_SIZE={world}: launch N>1 with torchrun"
+    return world, rank, local
+
+
+def max_over_ranks(ms, world):
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+# --------------------------------------------------------------------------- our arm
+def make_layer(shard, dev):
+    """The rank's slice of the layer: all heads of its batch rows, or some heads of one batch row."""
+    from lookahead_keys_attention_b200 import Castle
+    torch.manual_seed(0)
+    full = Castle(CFG["dim"], heads=CFG["heads"], dim_head=CFG["dim_head"])
+    hs = shard.h1 - shard.h0
+    m = Castle(CFG["dim"], heads=hs, dim_head=CFG["dim_head"])
+    d = CFG["dim_head"]
+    with torch.no_grad():
+        w = full.to_all_qkv.weight.view(6, CFG["heads"], d, CFG["dim"])[:, shard.h0:shard.h1]
+        m.to_all_qkv.weight.copy_(w.reshape(6 * hs * d, CFG["dim"]))
+        m.combine_heads.weight.copy_(full.combine_heads.weight[:, shard.h0 * d:shard.h1 * d])
+    return m.to(dev).bfloat16()
+
+
+def run_ours(args):
+    world, rank, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    from lookahead_keys_attention_b200 import _lib, castle_attention, check_status
+    from lookahead_keys_attention_b200.sharding import partition
+    lib = _lib.load()
+    peaks = load_peaks()
+    B, N, H, d, dim = (CFG[k] for k in ("batch", "seq_len", "heads", "dim_head", "dim"))
+    shard = partition(B, H, world, rank)
+    bs, hs = shard.b1 - shard.b0, shard.h1 - shard.h0
+    layer = make_layer(shard, dev)
+    g = torch.Generator().manual_seed(1)
+    x_host = torch.randn(B, N, dim, generator=g).bfloat16()[shard.b0:shard.b1].contiguous().pin_memory()
+    g_host = torch.randn(B, N, dim, generator=g).bfloat16()[shard.b0:shard.b1].contiguous().pin_memory()
+
+    # ---- core arm: q/k/v resident in HBM, as views of the packed projection output
+    with torch.no_grad():
+        packed = layer.to_all_qkv(x_host.to(dev)).view(bs, N, 6, hs, d)
+    packed.requires_grad_()
+    qu, ku, vu, qc, kc, vc = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(6))
+    gcore = torch.randn(bs, N, hs, d, device=dev, generator=torch.Generator(dev).manual_seed(2)).bfloat16().permute(0, 2, 1, 3)
+    scale = d ** -0.5
+
+    def core_step():
+        packed.grad = None
+        out = castle_attention(qc, kc, vc, qu, ku, vu, scale, False)
+        out.backward(gcore)
+
+    for _ in range(args.warmup):
+        core_step()
+    torch.cuda.synchronize()
+    check_status()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    for row in ev:
+        for e in row:
+            e.record()  # torch creates the underlying cudaEvent_t lazily; the library records into it later
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    with ClockSampler(local) as clocks:
+        e0.record()
+        for s in range(args.steps):
+            lib.castle_set_kernel_events(0, ev[s][0].cuda_event, ev[s][1].cuda_event)
+            lib.castle_set_kernel_events(1, ev[s][2].cuda_event, ev[s][3].cuda_event)
+            core_step()
+        e1.record()
+        barrier(world)
+    lib.castle_set_kernel_events(0, None, None)
+    lib.castle_set_kernel_events(1, None, None)
+    check_status()
+    ms_core = max_over_ranks(e0.elapsed_time(e1) / args.steps, world)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    bwd_ms = sum(e[2].elapsed_time(e[3]) for e in ev) / args.steps
+    f_fwd, f_bwd = core_flops(B, H, N, d)
+    value = (f_fwd + f_bwd) / (ms_core * 1e-3) / 1e12
+    rank_f_fwd, rank_f_bwd = core_flops(bs, hs, N, d)
+    bwd_tflops = rank_f_bwd / (bwd_ms * 1e-3) / 1e12
+    fwd_tflops = rank_f_fwd / (fwd_ms * 1e-3) / 1e12
+
+    # ---- end-to-end arm: the module called with host tensors
+    out_host = torch.empty(bs, N, dim, dtype=torch.bfloat16).pin_memory()
+    dx_host = torch.empty(bs, N, dim, dtype=torch.bfloat16).pin_memory()
+    group = None
+    if world > B:  # ranks that share a batch row hold different heads: their projections' outputs add up
+        import torch.distributed as dist
+        per = world // B
+        for b in range(B):
+            grp = dist.new_group(list(range(b * per, (b + 1) * per)))
+            if b == shard.b0:
+                group = grp
+
+    def e2e_step():
+        x = x_host.to(dev, non_blocking=True).requires_grad_()
+        gg = g_host.to(dev, non_blocking=True)
+        for p_ in layer.parameters():
+            p_.grad = None
+        out = layer(x)
+        out.backward(gg)
+        dx, o = x.grad, out.detach()
+        if group is not None:
+            import torch.distributed as dist
+            dist.all_reduce(o, group=group)
+            dist.all_reduce(dx, group=group)
+        out_host.copy_(o, non_blocking=True)
+        dx_host.copy_(dx, non_blocking=True)
+
+    for _ in range(args.warmup):
+        e2e_step()
+    barrier(world)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier(world)
+    check_status()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps, world)
+    e2e_value = (f_fwd + f_bwd) / (ms_e2e * 1e-3) / 1e12
+
+    line = {
+        "metric": "castle_attn_fwd_bwd_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_core, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "castle_attention_layer B=4 N=4096 H=16 d_head=64 dim=1024, forward+backward",
+                   "sharding": f"batch x head rectangles, {bs}x{hs} pairs per GPU", "flops": "19*B*H*N^2*d algorithmic",
+                   "l2": "inputs_exceed_l2 (q/k/v, grads and scratch of one step are > 126 MB)"},
+        "frac_of_tensor_peak": round(value / (peaks["tflops"] * world), 4),
+        "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(ms_e2e, 4),
+                "h2d_bytes_per_step": 2 * x_host.numel() * 2 * world, "d2h_bytes_per_step": 2 * out_host.numel() * 2 * world},
+        "gpu_launches": 5 * args.steps,
+        "kernels": {"fwd_main_ms": round(fwd_ms, 4), "fwd_main_tflops": round(fwd_tflops, 2),
+                    "bwd_main_ms": round(bwd_ms, 4), "bwd_main_tflops": round(bwd_tflops, 2)},
+        "roofline": {"kernel": "castle_bwd_kernel", "bound": "tensor", "achieved": round(bwd_tflops, 2),
+                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(bwd_tflops / peaks["tflops"], 4),
+                     "traffic": None, "peak_source": f"{peaks['source']} bf16 burst"},
+        "clocks": clocks.summary(),
+    }
+    if rank == 0 and world == 1:
+        line["cpu_baseline"] = cpu_baseline(steps=2, warmup=1)
+    if not args.no_decode:
+        dec = run_decode(args, world, rank, dev, peaks)
+        if rank == 0:
+            line["decode"] = dec
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def run_decode(args, world, rank, dev, peaks):
+    """Cached decode: B=64 (split by batch over ranks), prefix prefilled through the parallel pass."""
+    from lookahead_keys_attention_b200 import Castle, _lib, check_status
+    lib = _lib.load()
+    c = DECODE_CFG
+    bs = c["batch"] // world
+    torch.manual_seed(3)
+    m = Castle(c["dim"], heads=c["heads"], dim_head=c["dim_head"], cache_headroom=c["steps"] + 8).to(dev).bfloat16()
+    gen = torch.Generator(dev).manual_seed(4 + rank)
+    steps, warm = c["steps"], 3
+    with torch.no_grad():
+        # prefill in batch slices so the packed projection of the prefix stays a few GB
+        caches = []
+        for b0 in range(0, bs, 8):
+            xb = torch.randn(min(8, bs - b0), c["prefix"], c["dim"], device=dev, generator=gen).bfloat16()
+            _, cb = m(xb, return_next_cache=True)
+            caches.append(cb)
+            del xb
+        # one capacity buffer per cache for the whole rank-local batch
+        cap = c["prefix"] + steps + warm + 8
+        bufs = [torch.empty(bs, c["heads"], cap, c["dim_head"], dtype=torch.bfloat16, device=dev) for _ in range(4)]
+        for i in range(4):
+            b0 = 0
+            for cb in caches:
+                n = cb[i].shape[0]
+                bufs[i][b0:b0 + n, :, :c["prefix"]].copy_(cb[i])
+                b0 += n
+        del caches
+        from lookahead_keys_attention_b200 import Cache
+        cache = Cache(*(b[:, :, :c["prefix"]] for b in bufs))
+        xs = torch.randn(steps + warm, bs, 1, c["dim"], device=dev, generator=gen).bfloat16()
+        for s in range(warm):
+            _, cache = m(xs[s], cache=cache)
+        torch.cuda.synchronize()
+        check_status()
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
+        for a, b in ev:
+            a.record(); b.record()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier(world)
+        e0.record()
+        for s in range(steps):
+            lib.castle_set_kernel_events(2, ev[s][0].cuda_event, ev[s][1].cuda_event)
+            _, cache = m(xs[warm + s], cache=cache)
+        e1.record()
+        barrier(world)
+        lib.castle_set_kernel_events(2, None, None)
+        check_status()
+    ms = max_over_ranks(e0.elapsed_time(e1) / steps, world)
+    kms = sum(a.elapsed_time(b) for a, b in ev) / steps
+    t_mean = c["prefix"] + warm + (steps - 1) / 2
+    alg_bytes = bs * c["heads"] * 5 * t_mean * c["dim_head"] * 2
+    gbs = alg_bytes / (kms * 1e-3) / 1e9
+    return {"metric": "decode_tokens_per_s", "value": round(c["batch"] / (ms * 1e-3), 1), "unit": "tokens/s",
+            "ms_per_step": round(ms, 4), "kernel_ms": round(kms, 4),
+            "config": {"workload": f"cached decode B={c['batch']} H={c['heads']} d_head={c['dim_head']} prefix={c['prefix']} steps={steps}",
+                       "per_gpu_batch": bs},
+            "roofline": {"kernel": "castle_decode_kernel", "bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm"],
+                         "unit": "GB/s", "frac": round(gbs / peaks["hbm"], 4), "traffic": None,
+                         "algorithmic_bytes_per_launch": int(alg_bytes), "peak_source": peaks["source"]}}
+
+
+# --------------------------------------------------------------------------- CPU oracle arm
+def cpu_sample_time(steps, warmup):
+    """Forward + backward of the oracle (the reference's PyTorch arithmetic, bf16) on a bounded
+    sample of the workload: 1 batch row x 2 heads at the full N=4096, d=64."""
+    from oracle import castle_oracle as O
+    N, d, hs = CFG["seq_len"], CFG["dim_head"], 2
+    torch.manual_seed(0)
+    t = [(torch.randn(1, hs, N, d) * 3 ** -0.5).bfloat16() for _ in range(6)]
+    g = torch.randn(1, hs, N, d).bfloat16()
+    scale = d ** -0.5
+
+    def step():
+        O.castle_parallel(*t, scale)
+        O.castle_parallel_bwd(*t, scale, g)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    f_fwd, f_bwd = core_flops(1, hs, N, d)
+    return dt, (f_fwd + f_bwd) / dt / 1e12, f"1 batch row x {hs} heads of the workload (N={N}, d={d}), bf16, oracle fwd + closed-form bwd"
+
+
+def cpu_baseline(steps, warmup):
+    dt, tf, sample = cpu_sample_time(steps, warmup)
+    return {"value": round(tf, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": sample, "s_per_sample": round(dt, 3)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warm = min(args.steps, 5), min(args.warmup, 1)
+    dt, tf, sample = cpu_sample_time(steps, warm)
+    line = {
+        "impl": "reference", "metric": "castle_attn_fwd_bwd_tflops", "value": round(tf, 5), "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": round(dt * 1e3, 2),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "castle_attention_layer B=4 N=4096 H=16 d_head=64 dim=1024, forward+backward",
+                   "flops": "19*B*H*N^2*d algorithmic"},
+        "cpu_baseline": {"value": round(tf, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(tf, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
