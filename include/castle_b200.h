@@ -116,6 +116,29 @@ int castle_decode_step(const castle_problem_t* p, int32_t cache_len, int32_t cap
                        const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache, const castle_tensor_t* out,
                        void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* ---- cached single-token step without caller scratch -----------------------
+ * (no counterpart in the reference)  Same step and same arguments as
+ * castle_decode_step(), minus the workspace: the split partials go to a fixed
+ * 520 KiB array built into the library, which every GPU that loads the library
+ * holds until the process exits.  Meant for hosts that cannot allocate device
+ * memory on the token path (an engine whose own arena already owns the device,
+ * or a non-torch host that binds only this ABI).  It calls no allocator of any
+ * kind.  Limit: batch * heads * row-splits <= 1024 and dim_head <= 128; larger
+ * problems are rejected (< 0) with a message naming the limit - use
+ * castle_decode_step() for those.  The first call on each device looks up the
+ * array's device address (cudaGetSymbolAddress, with that device current); make
+ * that first call before starting any stream capture.  All calls on a device
+ * share the one array, so two calls whose kernels overlap on the GPU (different
+ * streams, or different host threads) race; calls on one stream are safe.
+ */
+int castle_decode_step_static(const castle_problem_t* p, int32_t cache_len, int32_t capacity,
+                              const castle_tensor_t* qc_new, const castle_tensor_t* kc_new,
+                              const castle_tensor_t* vc_new, const castle_tensor_t* qu_new,
+                              const castle_tensor_t* ku_new, const castle_tensor_t* vu_new,
+                              const castle_tensor_t* u_cache, const castle_tensor_t* qu_cache,
+                              const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache,
+                              const castle_tensor_t* out, int32_t* status, void* stream);
+
 /* ---- measurement aid ------------------------------------------------------
  * (no counterpart in the reference)  Bracket the MAIN kernel of later calls (from
  * any host thread of the process) with two caller-owned CUDA events recorded on the launch

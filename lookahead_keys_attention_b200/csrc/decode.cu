@@ -321,3 +321,80 @@ extern "C" int castle_decode_step(const castle_problem_t* p, int32_t cache_len, 
     default: return launch_decode_d<float>(dp, BH, p->dim_head, st);
   }
 }
+
+// ---------------------------------------------------------------------------
+// Decode step for hosts that may not allocate device memory on the token path.
+//
+// Some callers of this library cannot hand over a scratch buffer: a serving
+// loop whose own arena took all device memory at start-up (so a cudaMalloc on
+// the token path would fail, and would stall the device even if it did not), or
+// a small non-torch host that binds only this C ABI and has no device allocator
+// of its own.  For them the split partials of the decode step live in a fixed
+// array inside the library image.  Every GPU that loads the library carries
+// this array (520 KiB) until the process exits.
+namespace castle {
+
+constexpr int kStaticMaxSlots = 1024;          // batch * heads * row-splits
+constexpr int kStaticSlotFloats = 2 + 128;     // (max, sum) + dim_head values, dim_head <= 128
+static __device__ __align__(256) float g_decode_static_scratch[kStaticMaxSlots * kStaticSlotFloats];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel may
+// use; the device address is looked up once per device and kept here.
+constexpr int kMaxDevices = 64;
+static float* g_decode_static_ptr[kMaxDevices] = {nullptr};
+
+}  // namespace castle
+
+extern "C" int castle_decode_step_static(const castle_problem_t* p, int32_t cache_len, int32_t capacity,
+                                         const castle_tensor_t* qc_new, const castle_tensor_t* kc_new,
+                                         const castle_tensor_t* vc_new, const castle_tensor_t* qu_new,
+                                         const castle_tensor_t* ku_new, const castle_tensor_t* vu_new,
+                                         const castle_tensor_t* u_cache, const castle_tensor_t* qu_cache,
+                                         const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache,
+                                         const castle_tensor_t* out, int32_t* status, void* stream) {
+  (void)status;
+  if (!p) return reject("castle_decode_step_static: null problem");
+  if (p->batch <= 0 || p->heads <= 0) return reject("castle_decode_step_static: empty batch/heads");
+  if (cache_len < 0 || cache_len >= capacity)
+    return reject("castle_decode_step_static: cache_len %d must be in [0, capacity %d)", cache_len, capacity);
+  if (p->dtype != CASTLE_BF16 && p->dtype != CASTLE_F16 && p->dtype != CASTLE_F32)
+    return reject("castle_decode_step_static: unknown dtype %d", p->dtype);
+  int rc = 0;
+  const castle_tensor_t* ts[11] = {qc_new, kc_new, vc_new, qu_new, ku_new, vu_new, u_cache, qu_cache, kc_cache, vc_cache, out};
+  const char* names[11] = {"qc_new", "kc_new", "vc_new", "qu_new", "ku_new", "vu_new", "u_cache", "qu_cache", "kc_cache", "vc_cache", "out"};
+  for (int i = 0; i < 11; ++i)
+    if (!tensor_ok(ts[i], p->dtype, names[i], &rc)) return rc;
+  const int BH = p->batch * p->heads;
+  const int nsplit = decode_nsplit(BH, cache_len);
+  if (p->dim_head > 128 || (int64_t)BH * nsplit > kStaticMaxSlots)
+    return reject("castle_decode_step_static: batch*heads*splits = %lld exceeds the built-in scratch of %d partials "
+                  "(dim_head <= 128); use castle_decode_step with a caller-owned workspace",
+                  (long long)BH * nsplit, kStaticMaxSlots);
+  // set-up, once per device, with that device current
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "castle_decode_step_static cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return reject("castle_decode_step_static: device ordinal %d not supported", dev);
+  if (g_decode_static_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_decode_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "castle_decode_step_static cudaGetSymbolAddress");
+    g_decode_static_ptr[dev] = ptr;
+  }
+  DecodeParams dp;
+  dp.qc = *qc_new; dp.kc = *kc_new; dp.vc = *vc_new; dp.qu = *qu_new; dp.ku = *ku_new; dp.vu = *vu_new;
+  dp.U = *u_cache; dp.quc = *qu_cache; dp.kcc = *kc_cache; dp.vcc = *vc_cache; dp.out = *out;
+  dp.H = p->heads; dp.t = cache_len; dp.scale = p->scale;
+  dp.nsplit = nsplit;
+  dp.rows_per_split = (cache_len + nsplit - 1) / nsplit;
+  if (dp.rows_per_split < 1) dp.rows_per_split = 1;
+  // Every partial slot the merge kernel reads is written by this same call first, so the
+  // array needs no clearing between calls even though it keeps the previous call's contents.
+  dp.part = g_decode_static_ptr[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (p->dtype) {
+    case CASTLE_BF16: return launch_decode_d<__nv_bfloat16>(dp, BH, p->dim_head, st);
+    case CASTLE_F16: return launch_decode_d<__half>(dp, BH, p->dim_head, st);
+    default: return launch_decode_d<float>(dp, BH, p->dim_head, st);
+  }
+}
