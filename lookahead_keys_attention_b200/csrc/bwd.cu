@@ -12,8 +12,9 @@
 // dkc, dvc and dqu of the key block accumulate in tensor memory as well and are
 // written once at the end.  The gradients indexed by the query/position block
 // (dqc, dvu, dku) are summed over key blocks with fp32 vector reductions into a
-// workspace that a last kernel scales and casts.  Thread r owns row r of every
-// accumulator; the soft-max statistics (lse, delta) are per-row registers.
+// workspace that a last kernel scales and casts.  A thread owns 32 consecutive
+// columns of one accumulator row; the soft-max statistics (lse, delta) of its
+// row sit in registers.
 //
 // Shared memory (224 KB) is time-shared: the 128x128 16-bit operands the
 // threads produce (gate A, masked T, P, dS, dSu, dZ, dT) rotate through four
@@ -39,8 +40,6 @@ struct BwdParams {
   castle_tensor_t dqc, dkc, dvc, dqu, dku, dvu;
   int32_t* status;
 };
-
-__device__ __forceinline__ float sigmoid_b(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
@@ -93,8 +92,12 @@ __global__ void castle_bwd_finish_kernel(const BwdParams p) {
   }
 }
 
+constexpr int kBwdThreads = 512;
+
+// 512 threads: warp w works on TMEM lanes 32*(w%4).. and on the 32-column chunk w/4 of a
+// 128-column accumulator, so thread (row, chunk) owns 32 values of every 128x128 tile.
 template <typename T, int D>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
                   const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
                   const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu,
@@ -109,6 +112,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   constexpr uint32_t ID_D_KM = make_idesc(128, D, FMT, false, true, false);
   constexpr uint32_t ID_D_KM_NEG = make_idesc(128, D, FMT, false, true, true);
   constexpr uint32_t ID_D_MM = make_idesc(128, D, FMT, true, true, false);
+  constexpr float kLog2e = 1.4426950408889634f;
   // tensor-memory columns
   constexpr uint32_t C_W = 0, C_G = 64, C_DKC = 128, C_DVC = 192, C_DQU = 256, C_S = 320, C_X = 448;
   constexpr uint32_t C_X2 = C_S, C_X3 = C_S + 64;
@@ -131,10 +135,13 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, cc = warp >> 2;
+  const int row = quarter * 32 + lane;
+  const int c0 = cc * 32;
   const int bh = blockIdx.x, K = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
-  const int k0 = K * kBlkB, krow = k0 + tid;
+  const int k0 = K * kBlkB, krow = k0 + row;
 
   if (tid == 0) {
     mbar_init(&bar_res, 1); mbar_init(&bar_load, 1); mbar_init(&bar_ku, 1); mbar_init(&bar_mma, 1);
@@ -146,7 +153,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
   volatile int* abortp = &abort_flag;
 
   if (tid == 0) {
@@ -155,18 +162,15 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     tma_load_4d(sKc, &m_kc, &bar_res, 0, k0, h, b);
   }
   // W_K starts as the forward's final state
-  {
-    const float* src = p.w_state + ((int64_t)bh * p.N + krow) * D;
-#pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
-      float v[32];
+  if (c0 < D) {
+    const float* src = p.w_state + ((int64_t)bh * p.N + krow) * D + c0;
+    float v[32];
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float4 q = (krow < p.N) ? *reinterpret_cast<const float4*>(src + c * 32 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
-      }
-      tmem_st32(trow + C_W + c * 32, v);
+    for (int j = 0; j < 32; j += 4) {
+      float4 q = (krow < p.N) ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
     }
+    tmem_st32(trow + C_W + c0, v);
     tmem_st_wait();
   }
   mbar_wait(&bar_res, 0, abortp);
@@ -177,7 +181,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   const uint32_t aQu = smem_u32(sQu), aKc = smem_u32(sKc), aQc = smem_u32(sQc), aVu = smem_u32(sVu),
                  aVc = smem_u32(sVc), adO = smem_u32(sdO), aKP = smem_u32(sKP), aVD = smem_u32(sVD),
                  aWb = smem_u32(sWb), aGb = smem_u32(sGb), aA = smem_u32(sA), aT = smem_u32(sT);
-  const float inv_scale = 1.f / p.scale;
+  const float sl2 = p.scale * kLog2e;
 
 #define MMA_WAIT()                       \
   mbar_wait(&bar_mma, ph_mma, abortp);   \
@@ -189,7 +193,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   __syncthreads();
 
   for (int I = p.nblk - 1; I >= K; --I) {
-    const int i0 = I * kBlkB, irow = i0 + tid;
+    const int i0 = I * kBlkB, irow = i0 + row;
     const bool diag = (I == K), first = (I == p.nblk - 1);
     const bool rvalid = irow < p.N;
     if (tid == 0) {
@@ -200,7 +204,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       tma_load_4d(sdO, &m_do, &bar_load, 0, i0, h, b);
       tma_load_4d(sKP, &m_ku, &bar_load, 0, i0, h, b);
     }
-    const float lse_i = rvalid ? p.lse[(int64_t)bh * p.N + irow] : 0.f;
+    const float lse_b = rvalid ? p.lse[(int64_t)bh * p.N + irow] * kLog2e : 0.f;
     const float delta_i = rvalid ? p.delta[(int64_t)bh * p.N + irow] : 0.f;
     mbar_wait(&bar_load, ph_load, abortp);
     ph_load ^= 1;
@@ -212,17 +216,17 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {  // gate A (rows k, columns j), zero unless j > k
+    {  // gate A (rows k, columns j), zero unless j > k
       float v[32];
-      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float a = sigmoid_b(v[j] * p.scale);
-        v[j] = (!diag || (i0 + c * 32 + j > krow)) ? a : 0.f;
+      for (int j = 0; j < 32; ++j) v[j] = sigmoid_t<T>(v[j] * p.scale);
+      if (diag) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j > row) ? v[j] : 0.f;
       }
-      store_row32<T>(sA, kPanelB, tid, c * 32, v);
+      store_row32<T>(sA, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
 
@@ -234,21 +238,19 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {  // masked T (rows i, columns j <= i), unscaled
+    {  // masked T (rows i, columns j <= i), unscaled
       float v[32];
-      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j <= tid) ? v[j] : 0.f;
-      store_row32<T>(sT, kPanelB, tid, c * 32, v);
+      for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
+      store_row32<T>(sT, kPanelB, row, c0, v);
     }
-#pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {  // 16-bit copy of the peeled state
+    if (c0 < D) {  // 16-bit copy of the peeled state
       float v[32];
-      tmem_ld32(trow + C_W + c * 32, v);
+      tmem_ld32(trow + C_W + c0, v);
       tmem_ld_wait();
-      store_row32<T>(sWb, kPanelB, tid, c * 32, v);
+      store_row32<T>(sWb, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
 
@@ -260,24 +262,23 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
-    uint32_t dpk[64];  // silu'(Su), later dSu, two 16-bit values per register
-    uint32_t ppk[64];  // P
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    uint32_t dpk[16];  // silu'(Su), later dSu, two 16-bit values per register
+    uint32_t ppk[16];  // P
+    {
       float v[32];
-      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
         float su0 = v[j] * p.scale, su1 = v[j + 1] * p.scale;
-        float g0 = sigmoid_b(su0), g1 = sigmoid_b(su1);
-        v[j] = -su0 * g0 * inv_scale;
-        v[j + 1] = -su1 * g1 * inv_scale;
-        dpk[c * 16 + j / 2] = Elem<T>::pack2(g0 * (1.f + su0 * (1.f - g0)), g1 * (1.f + su1 * (1.f - g1)));
+        float g0 = sigmoid_t<T>(su0), g1 = sigmoid_t<T>(su1);
+        v[j] = -v[j] * g0;          // -silu(su) / scale
+        v[j + 1] = -v[j + 1] * g1;
+        dpk[j / 2] = Elem<T>::pack2(g0 * (1.f + su0 * (1.f - g0)), g1 * (1.f + su1 * (1.f - g1)));
       }
-      tmem_st32(trow + C_S + c * 32, v);
+      tmem_st32(trow + C_S + c0, v);
+      tmem_st_wait();
     }
-    tmem_st_wait();
     tc_fence_before();
     __syncthreads();
 
@@ -288,19 +289,23 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {  // P = exp(S - lse) (rows i, columns k); into slot 4 over Ku
+    {  // P = exp(S - lse) (rows i, columns k); into slot 4 over Ku
       float v[32];
-      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        bool ok0 = rvalid && (!diag || (c * 32 + j <= tid)), ok1 = rvalid && (!diag || (c * 32 + j + 1 <= tid));
-        v[j] = ok0 ? __expf(v[j] * p.scale - lse_i) : 0.f;
-        v[j + 1] = ok1 ? __expf(v[j + 1] * p.scale - lse_i) : 0.f;
-        ppk[c * 16 + j / 2] = Elem<T>::pack2(v[j], v[j + 1]);
+      for (int j = 0; j < 32; ++j) v[j] = ex2_approx(fmaf(v[j], sl2, -lse_b));
+      if (diag) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
       }
-      store_row32<T>(sKP, kPanelB, tid, c * 32, v);
+      if (!rvalid) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) ppk[j / 2] = Elem<T>::pack2(v[j], v[j + 1]);
+      store_row32<T>(sKP, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
 
@@ -316,20 +321,19 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mbar_expect_tx(&bar_ku, OPB);
       tma_load_4d(sKP, &m_ku, &bar_ku, 0, i0, h, b);
     }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {  // dS = P * (dP - delta) -> slot 3 (over Vc|dO); dSu = -dS * silu'(Su) stays in registers
+    {  // dS = P * (dP - delta) -> slot 3 (over Vc|dO); dSu = -dS * silu'(Su) stays in registers
       float v[32];
-      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
-        float2 pp = Elem<T>::unpack2(ppk[c * 16 + j / 2]);
-        float2 dd = Elem<T>::unpack2(dpk[c * 16 + j / 2]);
+        float2 pp = Elem<T>::unpack2(ppk[j / 2]);
+        float2 dd = Elem<T>::unpack2(dpk[j / 2]);
         float ds0 = pp.x * (v[j] - delta_i), ds1 = pp.y * (v[j + 1] - delta_i);
         v[j] = ds0; v[j + 1] = ds1;
-        dpk[c * 16 + j / 2] = Elem<T>::pack2(-ds0 * dd.x, -ds1 * dd.y);
+        dpk[j / 2] = Elem<T>::pack2(-ds0 * dd.x, -ds1 * dd.y);
       }
-      store_row32<T>(sVD, kPanelB, tid, c * 32, v);
+      store_row32<T>(sVD, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
 
@@ -341,14 +345,13 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
+    {  // dSu -> slot 3
+      uint8_t* panel = sVD + (c0 >> 6) * kPanelB;
+      const uint32_t chunk0 = (c0 & 63) >> 3;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {  // dSu -> slot 3
-      uint8_t* panel = sVD + (c >> 1) * kPanelB;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint4 w = make_uint4(dpk[c * 16 + q * 4], dpk[c * 16 + q * 4 + 1], dpk[c * 16 + q * 4 + 2], dpk[c * 16 + q * 4 + 3]);
-        *reinterpret_cast<uint4*>(panel + swz_off(tid, (c & 1) * 4 + q)) = w;
-      }
+      for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<uint4*>(panel + swz_off(row, chunk0 + q)) =
+            make_uint4(dpk[q * 4], dpk[q * 4 + 1], dpk[q * 4 + 2], dpk[q * 4 + 3]);
     }
     SMEM_TO_MMA_SYNC();
 
@@ -361,15 +364,14 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {  // dZ = dA * A * (1 - A) -> slot 2 (over Tm)
+    {  // dZ = dA * A * (1 - A) -> slot 2 (over Tm)
       float v[32], a[32];
-      tmem_ld32(trow + C_S + c * 32, v);
-      load_row32<T>(sA, kPanelB, tid, c * 32, a);
+      tmem_ld32(trow + C_S + c0, v);
+      load_row32<T>(sA, kPanelB, row, c0, a);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = v[j] * p.scale * a[j] * (1.f - a[j]);
-      store_row32<T>(sT, kPanelB, tid, c * 32, v);
+      store_row32<T>(sT, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
 
@@ -384,14 +386,13 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     }
     ph_ku ^= 1;
     MMA_WAIT();
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {  // masked dT (rows i, columns j <= i) -> slot 3 (over dSu)
+    {  // masked dT (rows i, columns j <= i) -> slot 3 (over dSu)
       float v[32];
-      tmem_ld32(trow + C_S + c * 32, v);
+      tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j <= tid) ? v[j] : 0.f;
-      store_row32<T>(sVD, kPanelB, tid, c * 32, v);
+      for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
+      store_row32<T>(sVD, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
 
@@ -405,60 +406,54 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
-    {
-      const int64_t rbase = ((int64_t)bh * p.N + irow) * D;
-      const uint32_t cols[3] = {C_X, C_X2, C_X3};
-      float* dsts[3] = {p.acc_dqc, p.acc_dvu, p.acc_dku};
-#pragma unroll
-      for (int t = 0; t < 3; ++t) {
+    if (cc < 3) {  // chunk groups 0,1,2: reduce dqc / dvu / dku of block I into the fp32 workspace
+      const uint32_t col = (cc == 0) ? C_X : (cc == 1 ? C_X2 : C_X3);
+      float* dst = ((cc == 0) ? p.acc_dqc : (cc == 1 ? p.acc_dvu : p.acc_dku)) + ((int64_t)bh * p.N + irow) * D;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          float v[32];
-          tmem_ld32(trow + cols[t] + c * 32, v);
-          tmem_ld_wait();
-          if (rvalid) {
+      for (int c = 0; c < D / 32; ++c) {
+        float v[32];
+        tmem_ld32(trow + col + c * 32, v);
+        tmem_ld_wait();
+        if (rvalid) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) red_add_v4(dsts[t] + rbase + c * 32 + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
-          }
+          for (int j = 0; j < 32; j += 4) red_add_v4(dst + c * 32 + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
         }
       }
-    }
+    } else {  // chunk group 3: 16-bit copy of G including block I, for the next (lower) block
 #pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {  // 16-bit copy of G including block I, for the next (lower) block
-      float v[32];
-      tmem_ld32(trow + C_G + c * 32, v);
-      tmem_ld_wait();
-      store_row32<T>(sGb, kPanelB, tid, c * 32, v);
+      for (int c = 0; c < D / 32; ++c) {
+        float v[32];
+        tmem_ld32(trow + C_G + c * 32, v);
+        tmem_ld_wait();
+        store_row32<T>(sGb, kPanelB, row, c * 32, v);
+      }
     }
     SMEM_TO_MMA_SYNC();
   }
 #undef MMA_WAIT
 #undef SMEM_TO_MMA_SYNC
 
-  // ---- key-block gradients: dkc (x scale), dvc, dqu (x scale)
-  {
+  // ---- key-block gradients: dkc (x scale), dvc, dqu (x scale); one chunk group each
+  if (cc < 3) {
     tc_fence_after();
-    const uint32_t cols[3] = {C_DKC, C_DVC, C_DQU};
-    const castle_tensor_t* dsts[3] = {&p.dkc, &p.dvc, &p.dqu};
-    const float mul[3] = {p.scale, 1.f, p.scale};
-#pragma unroll
-    for (int t = 0; t < 3; ++t) {
-      T* dst = reinterpret_cast<T*>(dsts[t]->ptr) + b * dsts[t]->stride_b + h * dsts[t]->stride_h + (int64_t)krow * dsts[t]->stride_n;
+    const uint32_t col = (cc == 0) ? C_DKC : (cc == 1 ? C_DVC : C_DQU);
+    const castle_tensor_t& dt = (cc == 0) ? p.dkc : (cc == 1 ? p.dvc : p.dqu);
+    const float mul = (cc == 1) ? 1.f : p.scale;
+    T* dst = reinterpret_cast<T*>(dt.ptr) + b * dt.stride_b + h * dt.stride_h + (int64_t)krow * dt.stride_n;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        float v[32];
-        tmem_ld32(trow + cols[t] + c * 32, v);
-        tmem_ld_wait();
-        if (krow < p.N) {
+    for (int c = 0; c < D / 32; ++c) {
+      float v[32];
+      tmem_ld32(trow + col + c * 32, v);
+      tmem_ld_wait();
+      if (krow < p.N) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 q;
-            q.x = Elem<T>::pack2(v[8 * j] * mul[t], v[8 * j + 1] * mul[t]);
-            q.y = Elem<T>::pack2(v[8 * j + 2] * mul[t], v[8 * j + 3] * mul[t]);
-            q.z = Elem<T>::pack2(v[8 * j + 4] * mul[t], v[8 * j + 5] * mul[t]);
-            q.w = Elem<T>::pack2(v[8 * j + 6] * mul[t], v[8 * j + 7] * mul[t]);
-            *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = q;
-          }
+        for (int j = 0; j < 4; ++j) {
+          uint4 q;
+          q.x = Elem<T>::pack2(v[8 * j] * mul, v[8 * j + 1] * mul);
+          q.y = Elem<T>::pack2(v[8 * j + 2] * mul, v[8 * j + 3] * mul);
+          q.z = Elem<T>::pack2(v[8 * j + 4] * mul, v[8 * j + 5] * mul);
+          q.w = Elem<T>::pack2(v[8 * j + 6] * mul, v[8 * j + 7] * mul);
+          *reinterpret_cast<uint4*>(dst + c * 32 + j * 8) = q;
         }
       }
     }
@@ -483,7 +478,7 @@ static int launch_bwd(const BwdParams& p, const CUtensorMap* maps, cudaStream_t 
   castle_bwd_delta_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
   dim3 grid(p.B * p.H, p.nblk);
   ev_start(CASTLE_KERNEL_BWD, st);
-  castle_bwd_kernel<T, D><<<grid, 128, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6]);
+  castle_bwd_kernel<T, D><<<grid, kBwdThreads, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6]);
   ev_stop(CASTLE_KERNEL_BWD, st);
   castle_bwd_finish_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
   e = cudaGetLastError();

@@ -10,8 +10,9 @@
 // (Z, W update, T, Su main, Su in-block term, Sc, P@Vc), all with fp32
 // accumulators in TMEM and 16-bit operands in 128-byte-swizzled shared memory,
 // either loaded by TMA (inputs) or written by the threads (sigmoid gate A,
-// masked T, the 16-bit copy of W, soft-max numerators P).  Thread r of the CTA
-// owns row r of every accumulator, so row maxima and sums need no shuffles.
+// masked T, the 16-bit copy of W, soft-max numerators P).  A thread owns 32
+// consecutive columns of one accumulator row; row maxima and sums of the four
+// threads sharing a row meet in shared memory.
 //
 // The soft-max over keys crosses CTAs, so each step emits an un-normalised
 // partial (row max, row sum, P@Vc) and a second kernel merges the partials of a
@@ -40,10 +41,12 @@ struct FwdParams {
 
 __host__ __device__ inline int64_t tri(int64_t i) { return i * (i + 1) / 2; }
 
-__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+constexpr int kFwdThreads = 512;
 
+// 512 threads: warp w works on TMEM lanes 32*(w%4).. (the hardware's rule) and on the
+// 32-column chunk w/4 of a 128-column accumulator, so thread (row, chunk) owns 32 values.
 template <typename T, int D>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
                   const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
                   const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu) {
@@ -55,6 +58,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   constexpr int FMT = Elem<T>::fmt;
   constexpr uint32_t ID_SQ = make_idesc(128, 128, FMT, false, false, false);
   constexpr uint32_t ID_D = make_idesc(128, D, FMT, false, true, false);
+  constexpr float kLog2e = 1.4426950408889634f;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -65,11 +69,18 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   uint8_t* sWb = sQc + OPB;
   uint8_t* sKuA = sWb + OPB;   // Ku[I], then the gate A[K,I], then the soft-max numerators P
   uint8_t* sVuT = sKuA + SQB;  // Vu[I], then the masked T[I,I]
+  // row max / row sum exchange between the four threads of a row: 4 KB over Qc[I], which is dead
+  // once the last product reading it (Sc) has completed and until the next step's TMA load
+  float (*red_max)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sQc);
+  float (*red_sum)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sQc + 4 * kBlk * sizeof(float));
   __shared__ uint64_t bar_res, bar_load, bar_mma;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, cc = warp >> 2;
+  const int row = quarter * 32 + lane;   // accumulator row (TMEM lane) of this thread
+  const int c0 = cc * 32;                // first of its 32 columns
   const int bh = blockIdx.x, K = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
   const int k0 = K * kBlk;
@@ -87,7 +98,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes
+  const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
   volatile int* abortp = &abort_flag;
 
   if (tid == 0) {
@@ -104,7 +115,8 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   uint32_t ph_load = 0, ph_mma = 0;
   const uint32_t aQu = smem_u32(sQu), aKc = smem_u32(sKc), aVc = smem_u32(sVc), aQc = smem_u32(sQc),
                  aWb = smem_u32(sWb), aKuA = smem_u32(sKuA), aVuT = smem_u32(sVuT);
-  const int krow = k0 + tid;  // global key index of this thread's row when rows are keys
+  const int krow = k0 + row;  // global key index of this thread's row when rows are keys
+  const float sl2 = p.scale * kLog2e;
 
   for (int I = K; I < p.nblk; ++I) {
     const int i0 = I * kBlk;
@@ -131,18 +143,17 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
-    // gate A = sigmoid(scale * Z), kept for j > k; written over Ku[I]
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    {  // gate A = sigmoid(scale * Z), kept for j > k; written over Ku[I]
       float v[32];
-      tmem_ld32(trow + COL_S + c * 32, v);
+      tmem_ld32(trow + COL_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float a = sigmoidf_fast(v[j] * p.scale);
-        v[j] = (!diag || (i0 + c * 32 + j > krow)) ? a : 0.f;
+      for (int j = 0; j < 32; ++j) v[j] = sigmoid_t<T>(v[j] * p.scale);
+      if (diag) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j > row) ? v[j] : 0.f;
       }
-      store_row32<T>(sKuA, kPanelBytes, tid, c * 32, v);
+      store_row32<T>(sKuA, kPanelBytes, row, c0, v);
     }
     fence_async_smem();
     tc_fence_before();
@@ -158,15 +169,13 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
-    // masked T (j <= i), unscaled, written over Vu[I]
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    {  // masked T (j <= i), unscaled, written over Vu[I]
       float v[32];
-      tmem_ld32(trow + COL_S + c * 32, v);
+      tmem_ld32(trow + COL_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = (c * 32 + j <= tid) ? v[j] : 0.f;
-      store_row32<T>(sVuT, kPanelBytes, tid, c * 32, v);
+      for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
+      store_row32<T>(sVuT, kPanelBytes, row, c0, v);
     }
     fence_async_smem();
     tc_fence_before();
@@ -182,27 +191,22 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
-    // penalty -silu(Su)/scale goes back into the accumulator; Sc is then accumulated on top of it
-    const float inv_scale = 1.f / p.scale;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    {  // penalty -silu(Su)/scale goes back into the accumulator; Sc is then accumulated on top of it
       float v[32];
-      tmem_ld32(trow + COL_S + c * 32, v);
+      tmem_ld32(trow + COL_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         float su = v[j] * p.scale;
-        v[j] = -su * sigmoidf_fast(su) * inv_scale;
+        v[j] = -v[j] * sigmoid_t<T>(su);   // = -silu(su) / scale
       }
-      tmem_st32(trow + COL_S + c * 32, v);
+      tmem_st32(trow + COL_S + c0, v);
     }
-    // refresh the 16-bit copy of W (now including block I) for the next step
-#pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
+    if (c0 < D) {  // refresh the 16-bit copy of W (now including block I) for the next step
       float v[32];
-      tmem_ld32(trow + COL_W + c * 32, v);
+      tmem_ld32(trow + COL_W + c0, v);
       tmem_ld_wait();
-      store_row32<T>(sWb, kPanelBytes, tid, c * 32, v);
+      store_row32<T>(sWb, kPanelBytes, row, c0, v);
     }
     tmem_st_wait();
     fence_async_smem();
@@ -218,34 +222,34 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
-    // row max, then P = exp(S - max) (rows = queries i, columns = keys k)
-    const int irow = i0 + tid;
-    float mrow = -INFINITY;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    // row max over the four column chunks, then P = exp(S - max) (rows = queries i, columns = keys k)
+    const int irow = i0 + row;
+    float mrow;
+    {
       float v[32];
-      tmem_ld32(trow + COL_S + c * 32, v);
+      tmem_ld32(trow + COL_S + c0, v);
       tmem_ld_wait();
+      if (diag) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        bool ok = !diag || (c * 32 + j <= tid);
-        mrow = fmaxf(mrow, ok ? v[j] * p.scale : -INFINITY);
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : -INFINITY;
       }
-    }
-    float lrow = 0.f;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      float v[32];
-      tmem_ld32(trow + COL_S + c * 32, v);
-      tmem_ld_wait();
+      float mx = v[0];
+#pragma unroll
+      for (int j = 1; j < 32; ++j) mx = fmaxf(mx, v[j]);
+      red_max[cc][row] = mx;
+      __syncthreads();
+      mx = fmaxf(fmaxf(red_max[0][row], red_max[1][row]), fmaxf(red_max[2][row], red_max[3][row]));
+      mrow = mx * p.scale;   // column 0 is never masked, so the maximum is finite
+      const float mb = mx * sl2;
+      float lsum = 0.f;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        bool ok = !diag || (c * 32 + j <= tid);
-        float pe = ok ? __expf(v[j] * p.scale - mrow) : 0.f;
-        lrow += pe;
+        float pe = ex2_approx(fmaf(v[j], sl2, -mb));   // exp(scale*v - max); masked entries give 0
+        lsum += pe;
         v[j] = pe;
       }
-      store_row32<T>(sKuA, kPanelBytes, tid, c * 32, v);
+      red_sum[cc][row] = lsum;
+      store_row32<T>(sKuA, kPanelBytes, row, c0, v);
     }
     fence_async_smem();
     tc_fence_before();
@@ -258,70 +262,66 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mma_commit(&bar_mma);
     }
     const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;
-    if (irow < p.N) {
-      float2* ml = reinterpret_cast<float2*>(p.part_ml) + tile * kBlk + tid;
+    if (cc == 0 && irow < p.N) {
+      float lrow = red_sum[0][row] + red_sum[1][row] + red_sum[2][row] + red_sum[3][row];
+      float2* ml = reinterpret_cast<float2*>(p.part_ml) + tile * kBlk + row;
       *ml = make_float2(mrow, lrow);
     }
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
-    {
-      float* dst = p.part_o + (tile * kBlk + tid) * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        float v[32];
-        tmem_ld32(trow + COL_O + c * 32, v);
-        tmem_ld_wait();
-        if (irow < p.N) {
+    if (c0 < D) {
+      float* dst = p.part_o + (tile * kBlk + row) * D + c0;
+      float v[32];
+      tmem_ld32(trow + COL_O + c0, v);
+      tmem_ld_wait();
+      if (irow < p.N) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(dst + c * 32 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        }
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
       }
     }
+    fence_async_smem();  // the exchange buffer over Qc[I] was read by threads; TMA writes it next
     tc_fence_before();
     __syncthreads();
   }
 
   // ---- W_K is now U[K]: the cache's lookahead keys and the backward's starting state
-  if (p.u_out.ptr != nullptr || p.w_state != nullptr) {
+  if ((p.u_out.ptr != nullptr || p.w_state != nullptr) && c0 < D) {
     tc_fence_after();
-#pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
-      float v[32];
-      tmem_ld32(trow + COL_W + c * 32, v);
-      tmem_ld_wait();
-      if (krow < p.N) {
-        if (p.w_state != nullptr) {
-          float* dst = p.w_state + ((int64_t)bh * p.N + krow) * D + c * 32;
+    float v[32];
+    tmem_ld32(trow + COL_W + c0, v);
+    tmem_ld_wait();
+    if (krow < p.N) {
+      if (p.w_state != nullptr) {
+        float* dst = p.w_state + ((int64_t)bh * p.N + krow) * D + c0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
+      if (p.u_out.ptr != nullptr) {
+        int64_t off = b * p.u_out.stride_b + h * p.u_out.stride_h + (int64_t)krow * p.u_out.stride_n + c0;
+        if (p.u_dtype == CASTLE_F32) {
+          float* dst = reinterpret_cast<float*>(p.u_out.ptr) + off;
 #pragma unroll
           for (int j = 0; j < 32; j += 4)
             *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        }
-        if (p.u_out.ptr != nullptr) {
-          int64_t off = b * p.u_out.stride_b + h * p.u_out.stride_h + (int64_t)krow * p.u_out.stride_n + c * 32;
-          if (p.u_dtype == CASTLE_F32) {
-            float* dst = reinterpret_cast<float*>(p.u_out.ptr) + off;
+        } else if (p.u_dtype == CASTLE_BF16) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.u_out.ptr) + off);
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else if (p.u_dtype == CASTLE_BF16) {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.u_out.ptr) + off);
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_uint4(Elem<__nv_bfloat16>::pack2(v[8 * j], v[8 * j + 1]),
+                                Elem<__nv_bfloat16>::pack2(v[8 * j + 2], v[8 * j + 3]),
+                                Elem<__nv_bfloat16>::pack2(v[8 * j + 4], v[8 * j + 5]),
+                                Elem<__nv_bfloat16>::pack2(v[8 * j + 6], v[8 * j + 7]));
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.u_out.ptr) + off);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              dst[j] = make_uint4(Elem<__nv_bfloat16>::pack2(v[8 * j], v[8 * j + 1]),
-                                  Elem<__nv_bfloat16>::pack2(v[8 * j + 2], v[8 * j + 3]),
-                                  Elem<__nv_bfloat16>::pack2(v[8 * j + 4], v[8 * j + 5]),
-                                  Elem<__nv_bfloat16>::pack2(v[8 * j + 6], v[8 * j + 7]));
-          } else {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.u_out.ptr) + off);
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              dst[j] = make_uint4(Elem<__half>::pack2(v[8 * j], v[8 * j + 1]),
-                                  Elem<__half>::pack2(v[8 * j + 2], v[8 * j + 3]),
-                                  Elem<__half>::pack2(v[8 * j + 4], v[8 * j + 5]),
-                                  Elem<__half>::pack2(v[8 * j + 6], v[8 * j + 7]));
-          }
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_uint4(Elem<__half>::pack2(v[8 * j], v[8 * j + 1]),
+                                Elem<__half>::pack2(v[8 * j + 2], v[8 * j + 3]),
+                                Elem<__half>::pack2(v[8 * j + 4], v[8 * j + 5]),
+                                Elem<__half>::pack2(v[8 * j + 6], v[8 * j + 7]));
         }
       }
     }
@@ -374,7 +374,7 @@ static int launch_fwd(const FwdParams& p, const CUtensorMap* maps, cudaStream_t 
   }
   dim3 grid(p.B * p.H, p.nblk);
   ev_start(CASTLE_KERNEL_FWD, st);
-  castle_fwd_kernel<T, D><<<grid, 128, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+  castle_fwd_kernel<T, D><<<grid, kFwdThreads, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
   ev_stop(CASTLE_KERNEL_FWD, st);
   constexpr int ROWS = 256 / (D / 4);
   dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);

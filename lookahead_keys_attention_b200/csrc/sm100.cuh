@@ -207,6 +207,25 @@ template <> struct Elem<__half> {
   static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
 };
 
+// ---------------------------------------------------------------- fast transcendentals
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// sigmoid at the precision of the operand type: one MUFU op (tanh) when the result is rounded
+// to bf16 anyway, exp + divide when it feeds fp16 operands (which carry three more mantissa bits)
+template <typename T>
+__device__ __forceinline__ float sigmoid_t(float x) {
+  if constexpr (Elem<T>::fmt == 1) return fmaf(0.5f, tanh_approx(0.5f * x), 0.5f);
+  else return __fdividef(1.f, 1.f + __expf(-x));
+}
+
 // Write 32 consecutive elements (columns c0..c0+31, c0 a multiple of 32) of row `row`
 // of a swizzled panel set whose panels are `panel_bytes` apart.
 template <typename T>
