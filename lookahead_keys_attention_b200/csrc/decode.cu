@@ -66,11 +66,20 @@ __device__ __forceinline__ float group_sum(float v) {
   return v;
 }
 
-constexpr int kDecodeThreads = 256;
-constexpr int kDecodeUnroll = 4;
+#ifndef CASTLE_DECODE_THREADS
+#define CASTLE_DECODE_THREADS 128
+#endif
+#ifndef CASTLE_DECODE_UNROLL
+#define CASTLE_DECODE_UNROLL 1
+#endif
+#ifndef CASTLE_DECODE_MIN_CTAS
+#define CASTLE_DECODE_MIN_CTAS 8
+#endif
+constexpr int kDecodeThreads = CASTLE_DECODE_THREADS;
+constexpr int kDecodeUnroll = CASTLE_DECODE_UNROLL;
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kDecodeThreads, 2) castle_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kDecodeThreads, CASTLE_DECODE_MIN_CTAS) castle_decode_kernel(const DecodeParams p) {
   constexpr int VEC = Vec<T>::N;
   constexpr int LPR = D / VEC;                 // lanes per row
   constexpr int RPW = 32 / LPR;                // rows per warp per pass
@@ -237,15 +246,33 @@ __global__ void castle_decode_merge_kernel(const DecodeParams p) {
   else o[c] = Elem<T>::from_f(aa / ll);
 }
 
-// Rows are split so that the grid has a few CTAs per SM even when batch*heads is small.
+// How many CTAs share the rows of one (batch, head) pair.  The kernel is bandwidth bound and runs
+// CASTLE_DECODE_MIN_CTAS CTAs per SM, so what matters is that the grid fills whole "waves" of
+// resident CTAs: pick the smallest split (at least 128 rows each, at most 64) whose last wave is
+// nearly full.
 static int decode_nsplit(int BH, int t) {
-  const int target_ctas = 148 * 4;
-  int ns = (target_ctas + BH - 1) / BH;
-  int max_by_rows = (t + 255) / 256;  // at least 256 rows per split
-  if (ns > max_by_rows) ns = max_by_rows;
-  if (ns < 1) ns = 1;
-  if (ns > 64) ns = 64;
-  return ns;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      sms = n;
+    else
+      sms = 148;
+  }
+  const int slots = sms * CASTLE_DECODE_MIN_CTAS;
+  int max_ns = t / 128;
+  if (max_ns > 64) max_ns = 64;
+  if (max_ns < 1) max_ns = 1;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int ns = 1; ns <= max_ns; ++ns) {
+    const long long total = (long long)BH * ns;
+    const long long waves = (total + slots - 1) / slots;
+    const double eff = (double)total / (double)(waves * slots);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = ns; }
+  }
+  return best;
 }
 
 template <typename T, int D>
