@@ -164,7 +164,7 @@ def run_ours(args):
     world, rank, local = dist_setup(args.gpus)
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    from lookahead_keys_attention_b200 import _lib, castle_attention, check_status
+    from lookahead_keys_attention_b200 import _lib, castle_attention_packed, check_status
     from lookahead_keys_attention_b200.sharding import partition
     lib = _lib.load()
     peaks = load_peaks()
@@ -180,13 +180,12 @@ def run_ours(args):
     with torch.no_grad():
         packed = layer.to_all_qkv(x_host.to(dev)).view(bs, N, 6, hs, d)
     packed.requires_grad_()
-    qu, ku, vu, qc, kc, vc = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(6))
     gcore = torch.randn(bs, N, hs, d, device=dev, generator=torch.Generator(dev).manual_seed(2)).bfloat16().permute(0, 2, 1, 3)
     scale = d ** -0.5
 
     def core_step():
         packed.grad = None
-        out = castle_attention(qc, kc, vc, qu, ku, vu, scale, False)
+        out = castle_attention_packed(packed, scale, False)
         out.backward(gcore)
 
     for _ in range(args.warmup):

@@ -4,6 +4,6 @@
 replaces the reference's `castle_attention_triton` operator.
 """
 from .castle import Cache, Castle
-from .ops import castle_attention, castle_decode_step, check_status
+from .ops import castle_attention, castle_attention_packed, castle_decode_step, check_status
 
-__all__ = ["Castle", "Cache", "castle_attention", "castle_decode_step", "check_status"]
+__all__ = ["Castle", "Cache", "castle_attention", "castle_attention_packed", "castle_decode_step", "check_status"]

@@ -19,7 +19,7 @@ from collections import namedtuple
 import torch
 from torch import nn
 
-from .ops import castle_attention, castle_decode_step
+from .ops import castle_attention, castle_attention_packed, castle_decode_step
 
 Cache = namedtuple("Cache", ("U", "qu_cache", "kc_cache", "vc_cache"))
 
@@ -94,21 +94,30 @@ class Castle(nn.Module):
         if return_next_cache is None:
             return_next_cache = is_inference
         x = self.norm(x)
-        qu, ku, vu, qc, kc, vc = self._split(self.to_all_qkv(x))
+        qkvs = self.to_all_qkv(x)
+        qu, ku, vu, qc, kc, vc = self._split(qkvs)
         if self.rotary_emb is not None:
             offset = cache.kc_cache.shape[-2] if cache is not None else 0
             qc, kc, qu, ku, vu = (self.rotary_emb.rotate(t, offset) for t in (qc, kc, qu, ku, vu))
 
         if not is_inference:
             assert cache is None, "must be inferencing single tokens if receiving cache"
+            packed = None
+            if self.rotary_emb is None:  # the kernels read the projection output in place
+                packed = qkvs.view(x.shape[0], seq_len, 6, self.heads, self.dim_head)
             if return_next_cache:
-                out, U = castle_attention(qc, kc, vc, qu, ku, vu, self.scale, True)
+                if packed is not None:
+                    out, U = castle_attention_packed(packed, self.scale, True)
+                else:
+                    out, U = castle_attention(qc, kc, vc, qu, ku, vu, self.scale, True)
                 # the cache lives in buffers with spare rows so that decode steps can append in place
                 bufs = self._new_buffers(U, seq_len)
                 with torch.no_grad():
                     for buf, src in zip(bufs, (U, qu, kc, vc)):
                         buf[:, :, :seq_len].copy_(src)
                 next_cache = Cache(*(buf[:, :, :seq_len] for buf in bufs))
+            elif packed is not None:
+                out = castle_attention_packed(packed, self.scale, False)
             else:
                 out = castle_attention(qc, kc, vc, qu, ku, vu, self.scale, False)
         else:

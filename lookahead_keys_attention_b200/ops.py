@@ -105,7 +105,7 @@ class _CastleAttention(torch.autograd.Function):
 
         ins = [prep(t) for t in (qc, kc, vc, qu, ku, vu)]
         dev = qc.device
-        need_grad = any(ctx.needs_input_grad[:6])
+        need_grad = any(ctx.needs_input_grad[:6]) if len(ctx.needs_input_grad) > 3 else ctx.needs_input_grad[0]
         # laid out (B, N, H, d): merging heads afterwards is a free reshape
         out = torch.empty(B, N, H, dp, dtype=cdtype, device=dev).permute(0, 2, 1, 3)
         lse = torch.empty(B, H, N, dtype=torch.float32, device=dev)
@@ -140,7 +140,7 @@ class _CastleAttention(torch.autograd.Function):
         return o
 
     @staticmethod
-    def backward(ctx, do, dU=None):
+    def backward(ctx, do, dU=None, packed_out=False):
         lib = _lib.load()
         qc, kc, vc, qu, ku, vu, out, lse, wst = ctx.saved_tensors
         B, H, N, dp = qc.shape
@@ -162,10 +162,37 @@ class _CastleAttention(torch.autograd.Function):
         rc = lib.castle_bwd(ctypes.byref(prob), *[ctypes.byref(x) for x in args], lse.data_ptr(), wst.data_ptr(),
                             *[ctypes.byref(x) for x in grads], ws.data_ptr(), ws.numel(), st.data_ptr(), _stream(dev))
         _lib.check(rc, "castle_bwd")
+        if packed_out:
+            g = packed[..., :d]
+            return g.to(ctx.orig_dtype) if ctx.orig_dtype != cdtype else g
         res = [g[..., :d] for g in (gqc, gkc, gvc, gqu, gku, gvu)]
         if ctx.orig_dtype != cdtype:
             res = [g.to(ctx.orig_dtype) for g in res]
         return (*res, None, None)
+
+
+class _CastleAttentionPacked(torch.autograd.Function):
+    """Same kernels, one autograd input: the packed projection output (B, N, 6, H, d) in the
+    order qu,ku,vu,qc,kc,vc.  Its gradient is the packed buffer the backward kernels write, so
+    autograd has nothing to scatter or sum (six separate view-gradients cost ~10 extra passes)."""
+
+    @staticmethod
+    def forward(ctx, packed, scale, return_U):
+        qu, ku, vu, qc, kc, vc = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(6))
+        inner = _CastleAttention
+        # run the six-view forward with this ctx standing in (it only stores tensors and scalars)
+        res = inner.forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U)
+        return res
+
+    @staticmethod
+    def backward(ctx, do, dU=None):
+        return _CastleAttention.backward(ctx, do, dU, packed_out=True), None, None
+
+
+def castle_attention_packed(packed, scale, return_U_for_cache=False):
+    """Parallel CASTLE attention on the packed projection output (B, N, 6, H, d), order
+    qu,ku,vu,qc,kc,vc (the layout `to_all_qkv` produces).  Returns out (B, H, N, d) [, U]."""
+    return _CastleAttentionPacked.apply(packed, scale, bool(return_U_for_cache))
 
 
 def castle_attention(qc, kc, vc, qu, ku, vu, scale, return_U_for_cache=False):

@@ -161,3 +161,21 @@ def test_backward_deterministic_forward_state():
     b = _grads(1, 2, 300, 64, torch.bfloat16, seed=11)
     for name in ("dkc", "dvc", "dqu"):
         assert torch.equal(a[name][0], b[name][0]), name
+
+
+def test_packed_operator_equals_six_view_operator():
+    from lookahead_keys_attention_b200 import castle_attention, castle_attention_packed
+    packed = (_inputs(2, 2, 300, 64, torch.float32, seed=5) * PROJ_STD).bfloat16().cuda()
+    g = torch.randn(2, 2, 300, 64, device="cuda").bfloat16()
+    a = packed.clone().requires_grad_()
+    qu, ku, vu, qc, kc, vc = _views(a)
+    oa, Ua = castle_attention(qc, kc, vc, qu, ku, vu, 0.125, True)
+    oa.backward(g)
+    b = packed.clone().requires_grad_()
+    ob, Ub = castle_attention_packed(b, 0.125, True)
+    ob.backward(g)
+    assert torch.equal(oa, ob) and torch.equal(Ua, Ub)
+    # dkc, dvc, dqu are bit-reproducible; dqc, dvu, dku are summed with fp32 atomics
+    assert torch.allclose(a.grad.float(), b.grad.float(), atol=1e-2, rtol=1e-2)
+    for i in (0, 4, 5):  # qu, kc, vc slots
+        assert torch.equal(a.grad[:, :, i], b.grad[:, :, i])
