@@ -245,23 +245,25 @@ def run_ours(args):
         out_host.copy_(o, non_blocking=True)
         dx_host.copy_(dx, non_blocking=True)
 
-    for _ in range(args.warmup):
-        e2e_step()
+    if not args.no_e2e:
+        for _ in range(args.warmup):
+            e2e_step()
     barrier(world)
     e0.record()
-    for _ in range(args.steps):
-        e2e_step()
+    if not args.no_e2e:
+        for _ in range(args.steps):
+            e2e_step()
     e1.record()
     barrier(world)
     check_status()
-    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps, world)
+    ms_e2e = max_over_ranks(max(e0.elapsed_time(e1), 1e-6) / args.steps, world)
     e2e_value = (f_fwd + f_bwd) / (ms_e2e * 1e-3) / 1e12
 
     line = {
         "metric": "castle_attn_fwd_bwd_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_core, 4), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "castle_attention_layer B=4 N=4096 H=16 d_head=64 dim=1024, forward+backward",
+        "config": {"workload": f"castle_attention_layer B={B} N={N} H={H} d_head={d} dim={dim}, forward+backward",
                    "sharding": f"batch x head rectangles, {bs}x{hs} pairs per GPU", "flops": "19*B*H*N^2*d algorithmic",
                    "l2": "inputs_exceed_l2 (q/k/v, grads and scratch of one step are > 126 MB)"},
         "frac_of_tensor_peak": round(value / (peaks["tflops"] * world), 4),
@@ -272,10 +274,15 @@ def run_ours(args):
                     "bwd_main_ms": round(bwd_ms, 4), "bwd_main_tflops": round(bwd_tflops, 2)},
         "roofline": {"kernel": "castle_bwd_kernel", "bound": "tensor", "achieved": round(bwd_tflops, 2),
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(bwd_tflops / peaks["tflops"], 4),
-                     "traffic": None, "peak_source": f"{peaks['source']} bf16 burst"},
+                     # dram read+write bytes per launch: ncu capture of the B=2 case (1.055 GB), which grows
+                     # in proportion to the (batch, head) pairs a launch processes
+                     "traffic": int(1.055e9 / 32 * bs * hs) if (N, d) == (4096, 64) else None,
+                     "peak_source": f"{peaks['source']} bf16 burst"},
         "clocks": clocks.summary(),
     }
-    if rank == 0 and world == 1:
+    if args.no_e2e:
+        line["e2e"] = None
+    if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(steps=2, warmup=1)
     if not args.no_decode:
         dec = run_decode(args, world, rank, dev, peaks)
@@ -408,7 +415,21 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end arm (profiling runs)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline (profiling runs)")
+    ap.add_argument("--batch", type=int, default=None, help="override B (smaller case of the same workload, for ncu)")
+    ap.add_argument("--seq-len", type=int, default=None, help="override N (for ncu captures)")
+    ap.add_argument("--decode-steps", type=int, default=None, help="override the number of decode steps (for ncu)")
+    ap.add_argument("--decode-batch", type=int, default=None, help="override the decode batch (for ncu)")
     args = ap.parse_args()
+    if args.batch:
+        CFG["batch"] = args.batch
+    if args.seq_len:
+        CFG["seq_len"] = args.seq_len
+    if args.decode_steps:
+        DECODE_CFG["steps"] = args.decode_steps
+    if args.decode_batch:
+        DECODE_CFG["batch"] = args.decode_batch
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
