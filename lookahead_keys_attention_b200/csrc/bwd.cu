@@ -11,7 +11,7 @@
 //        contribute to d(loss)/d(W_K); it yields dA and dvu for block I.
 // dkc, dvc and dqu of the key block accumulate in tensor memory as well and are
 // written once at the end.  The gradients indexed by the query/position block
-// (dqc, dvu, dku) are summed over key blocks with fp32 vector reductions into a
+// (dqc, dvu, dku) are summed over key blocks with TMA reduce-adds (fp32) into a
 // workspace that a last kernel scales and casts.  A thread owns 32 consecutive
 // columns of one accumulator row; the soft-max statistics (lse, delta) of its
 // row sit in registers.
@@ -39,11 +39,10 @@ struct BwdParams {
   castle_tensor_t out, dout;
   castle_tensor_t dqc, dkc, dvc, dqu, dku, dvu;
   int32_t* status;
+#ifdef CASTLE_PHASE_TIMING
+  long long* timing;
+#endif
 };
-
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 // delta[b,h,i] = sum_d out * dout  (lookahead_keys_attention_triton.py:175-214 in the reference)
 template <typename T, int D>
@@ -94,6 +93,14 @@ __global__ void castle_bwd_finish_kernel(const BwdParams p) {
 
 constexpr int kBwdThreads = 512;
 
+// Optional phase timing (debug builds only): thread 0 of CTA (0,0) stores clock64() at each phase
+// boundary of its first steps behind the fp32 workspace, which the host dumps.
+#ifdef CASTLE_PHASE_TIMING
+#define BPHASE_MARK(i) do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && tstep < 8) p.timing[tstep * 32 + (i)] = clock64(); } while (0)
+#else
+#define BPHASE_MARK(i) do { } while (0)
+#endif
+
 // 512 threads: warp w works on TMEM lanes 32*(w%4).. and on the 32-column chunk w/4 of a
 // 128-column accumulator, so thread (row, chunk) owns 32 values of every 128x128 tile.
 template <typename T, int D>
@@ -101,7 +108,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
                   const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
                   const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu,
-                  const __grid_constant__ CUtensorMap m_do) {
+                  const __grid_constant__ CUtensorMap m_do, const __grid_constant__ CUtensorMap m_acc_dqc,
+                  const __grid_constant__ CUtensorMap m_acc_dvu, const __grid_constant__ CUtensorMap m_acc_dku) {
   static_assert(D == 64, "this kernel is laid out for dim_head 64");
   constexpr uint32_t OPB = kPanelB;          // one d-wide operand tile (16 KB)
   constexpr uint32_t SQB = 2 * kPanelB;      // one 128x128 tile (32 KB)
@@ -131,7 +139,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   uint8_t* sGb = sWb + OPB;
   uint8_t* sA = sGb + OPB;             // slot 1: gate A
   uint8_t* sT = sA + SQB;              // slot 2: masked T, later dZ
-  __shared__ uint64_t bar_res, bar_load, bar_ku, bar_mma;
+  __shared__ uint64_t bar_res, bar_load, bar_vd, bar_ku, bar_mma;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -144,7 +152,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   const int k0 = K * kBlkB, krow = k0 + row;
 
   if (tid == 0) {
-    mbar_init(&bar_res, 1); mbar_init(&bar_load, 1); mbar_init(&bar_ku, 1); mbar_init(&bar_mma, 1);
+    mbar_init(&bar_res, 1); mbar_init(&bar_load, 1); mbar_init(&bar_vd, 1); mbar_init(&bar_ku, 1); mbar_init(&bar_mma, 1);
     mbar_fence_init();
     abort_flag = 0;
   }
@@ -160,6 +168,11 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     mbar_expect_tx(&bar_res, 2 * OPB);
     tma_load_4d(sQu, &m_qu, &bar_res, 0, k0, h, b);
     tma_load_4d(sKc, &m_kc, &bar_res, 0, k0, h, b);
+    // first step's Qc, Vu, Ku; later steps prefetch theirs at the end of the step before
+    mbar_expect_tx(&bar_load, 3 * OPB);
+    tma_load_4d(sQc, &m_qc, &bar_load, 0, (p.nblk - 1) * kBlkB, h, b);
+    tma_load_4d(sVu, &m_vu, &bar_load, 0, (p.nblk - 1) * kBlkB, h, b);
+    tma_load_4d(sKP, &m_ku, &bar_load, 0, (p.nblk - 1) * kBlkB, h, b);
   }
   // W_K starts as the forward's final state
   if (c0 < D) {
@@ -177,7 +190,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   tc_fence_before();
   __syncthreads();
 
-  uint32_t ph_load = 0, ph_ku = 0, ph_mma = 0;
+  uint32_t ph_load = 0, ph_vd = 0, ph_ku = 0, ph_mma = 0;
   const uint32_t aQu = smem_u32(sQu), aKc = smem_u32(sKc), aQc = smem_u32(sQc), aVu = smem_u32(sVu),
                  aVc = smem_u32(sVc), adO = smem_u32(sdO), aKP = smem_u32(sKP), aVD = smem_u32(sVD),
                  aWb = smem_u32(sWb), aGb = smem_u32(sGb), aA = smem_u32(sA), aT = smem_u32(sT);
@@ -196,26 +209,25 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     const int i0 = I * kBlkB, irow = i0 + row;
     const bool diag = (I == K), first = (I == p.nblk - 1);
     const bool rvalid = irow < p.N;
-    if (tid == 0) {
-      mbar_expect_tx(&bar_load, 5 * OPB);
-      tma_load_4d(sQc, &m_qc, &bar_load, 0, i0, h, b);
-      tma_load_4d(sVu, &m_vu, &bar_load, 0, i0, h, b);
-      tma_load_4d(sVc, &m_vc, &bar_load, 0, k0, h, b);
-      tma_load_4d(sdO, &m_do, &bar_load, 0, i0, h, b);
-      tma_load_4d(sKP, &m_ku, &bar_load, 0, i0, h, b);
-    }
+#ifdef CASTLE_PHASE_TIMING
+    const int tstep = p.nblk - 1 - I;
+#endif
+    BPHASE_MARK(0);
+
     const float lse_b = rvalid ? p.lse[(int64_t)bh * p.N + irow] * kLog2e : 0.f;
     const float delta_i = rvalid ? p.delta[(int64_t)bh * p.N + irow] : 0.f;
     mbar_wait(&bar_load, ph_load, abortp);
     ph_load ^= 1;
+    BPHASE_MARK(1);
 
     // ---- M1: Z = Qu[K] @ Ku[I]^T
     if (tid == 0) {
       tc_fence_after();
-      gemm_kk(tmem + C_S, aQu, kPanelB, aKP, kPanelB, 1, ID_SQ_KK, false);
+      gemm_kk_t<1>(tmem + C_S, aQu, aKP, ID_SQ_KK, false);
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
+    BPHASE_MARK(2);
     {  // gate A (rows k, columns j), zero unless j > k
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -229,15 +241,24 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       store_row32<T>(sA, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
+    BPHASE_MARK(3);
 
     // ---- M2: peel W_K -= A @ Vu[I];  T = Qc[I] @ Vu[I]^T
     if (tid == 0) {
       tc_fence_after();
-      gemm_km(tmem + C_W, aA, kPanelB, aVu, kPanelB, 8, ID_D_KM_NEG, true);
-      gemm_kk(tmem + C_S, aQc, kPanelB, aVu, kPanelB, 1, ID_SQ_KK, false);
+      // The reduce of the step before must have finished reading its staging tiles before they are
+      // written again: slot 2 and Wb by the threads once this phase's products are done, Vc|dO by
+      // the loads issued here (they are needed at the fifth phase).
+      bulk_wait_read0();
+      mbar_expect_tx(&bar_vd, 2 * OPB);
+      tma_load_4d(sVc, &m_vc, &bar_vd, 0, k0, h, b);
+      tma_load_4d(sdO, &m_do, &bar_vd, 0, i0, h, b);
+      gemm_km_t<8>(tmem + C_W, aA, aVu, ID_D_KM_NEG, true);
+      gemm_kk_t<1>(tmem + C_S, aQc, aVu, ID_SQ_KK, false);
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
+    BPHASE_MARK(4);
     {  // masked T (rows i, columns j <= i), unscaled
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -253,15 +274,17 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       store_row32<T>(sWb, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
+    BPHASE_MARK(5);
 
     // ---- M3: Su/scale = Qc[I] @ Wb^T + Tm @ A^T
     if (tid == 0) {
       tc_fence_after();
-      if (!diag) gemm_kk(tmem + C_S, aQc, kPanelB, aWb, kPanelB, 1, ID_SQ_KK, false);
-      gemm_kk(tmem + C_S, aT, kPanelB, aA, kPanelB, 2, ID_SQ_KK, !diag);
+      if (!diag) gemm_kk_t<1>(tmem + C_S, aQc, aWb, ID_SQ_KK, false);
+      gemm_kk_t<2>(tmem + C_S, aT, aA, ID_SQ_KK, !diag);
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
+    BPHASE_MARK(6);
     uint32_t dpk[16];  // silu'(Su), later dSu, two 16-bit values per register
     uint32_t ppk[16];  // P
     {
@@ -281,14 +304,16 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     }
     tc_fence_before();
     __syncthreads();
+    BPHASE_MARK(7);
 
     // ---- M4: S/scale = penalty + Qc[I] @ Kc[K]^T
     if (tid == 0) {
       tc_fence_after();
-      gemm_kk(tmem + C_S, aQc, kPanelB, aKc, kPanelB, 1, ID_SQ_KK, true);
+      gemm_kk_t<1>(tmem + C_S, aQc, aKc, ID_SQ_KK, true);
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
+    BPHASE_MARK(8);
     {  // P = exp(S - lse) (rows i, columns k); into slot 4 over Ku
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -308,15 +333,19 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       store_row32<T>(sKP, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
+    BPHASE_MARK(9);
 
     // ---- M5: dvc += P^T @ dO[I];  dP = dO[I] @ Vc[K]^T
     if (tid == 0) {
       tc_fence_after();
-      gemm_mm(tmem + C_DVC, aKP, kPanelB, adO, kPanelB, 8, ID_D_MM, !first);
-      gemm_kk(tmem + C_S, adO, kPanelB, aVc, kPanelB, 1, ID_SQ_KK, false);
+      mbar_wait(&bar_vd, ph_vd, abortp);
+      gemm_mm_t<8>(tmem + C_DVC, aKP, adO, ID_D_MM, !first);
+      gemm_kk_t<1>(tmem + C_S, adO, aVc, ID_SQ_KK, false);
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
+    BPHASE_MARK(10);
+    ph_vd ^= 1;
     if (tid == 0) {  // P is consumed: bring Ku[I] back for the dqu product
       mbar_expect_tx(&bar_ku, OPB);
       tma_load_4d(sKP, &m_ku, &bar_ku, 0, i0, h, b);
@@ -336,15 +365,17 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       store_row32<T>(sVD, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
+    BPHASE_MARK(11);
 
     // ---- M6: dkc += dS^T @ Qc[I];  X = dS @ Kc[K]
     if (tid == 0) {
       tc_fence_after();
-      gemm_mm(tmem + C_DKC, aVD, kPanelB, aQc, kPanelB, 8, ID_D_MM, !first);
-      gemm_km(tmem + C_X, aVD, kPanelB, aKc, kPanelB, 8, ID_D_KM, false);
+      gemm_mm_t<8>(tmem + C_DKC, aVD, aQc, ID_D_MM, !first);
+      gemm_km_t<8>(tmem + C_X, aVD, aKc, ID_D_KM, false);
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
+    BPHASE_MARK(12);
     {  // dSu -> slot 3
       uint8_t* panel = sVD + (c0 >> 6) * kPanelB;
       const uint32_t chunk0 = (c0 & 63) >> 3;
@@ -354,16 +385,18 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
             make_uint4(dpk[q * 4], dpk[q * 4 + 1], dpk[q * 4 + 2], dpk[q * 4 + 3]);
     }
     SMEM_TO_MMA_SYNC();
+    BPHASE_MARK(13);
 
     // ---- M7: X += dSu @ Wb;  dA/scale = Gb @ Vu[I]^T + dSu^T @ Tm   (rows k, columns j)
     if (tid == 0) {
       tc_fence_after();
-      if (!diag) gemm_km(tmem + C_X, aVD, kPanelB, aWb, kPanelB, 8, ID_D_KM, true);
-      if (!first) gemm_kk(tmem + C_S, aGb, kPanelB, aVu, kPanelB, 1, ID_SQ_KK, false);
-      gemm_mm(tmem + C_S, aVD, kPanelB, aT, kPanelB, 8, ID_SQ_MM, !first);
+      if (!diag) gemm_km_t<8>(tmem + C_X, aVD, aWb, ID_D_KM, true);
+      if (!first) gemm_kk_t<1>(tmem + C_S, aGb, aVu, ID_SQ_KK, false);
+      gemm_mm_t<8>(tmem + C_S, aVD, aT, ID_SQ_MM, !first);
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
+    BPHASE_MARK(14);
     {  // dZ = dA * A * (1 - A) -> slot 2 (over Tm)
       float v[32], a[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -374,18 +407,20 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       store_row32<T>(sT, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
+    BPHASE_MARK(15);
 
     // ---- M8: G += dSu^T @ Qc[I];  dT = dSu @ A;  dqu += dZ @ Ku[I]
     if (tid == 0) {
       tc_fence_after();
-      gemm_mm(tmem + C_G, aVD, kPanelB, aQc, kPanelB, 8, ID_D_MM, !first);
-      gemm_km(tmem + C_S, aVD, kPanelB, aA, kPanelB, 8, ID_SQ_KM, false);
+      gemm_mm_t<8>(tmem + C_G, aVD, aQc, ID_D_MM, !first);
+      gemm_km_t<8>(tmem + C_S, aVD, aA, ID_SQ_KM, false);
       mbar_wait(&bar_ku, ph_ku, abortp);
-      gemm_km(tmem + C_DQU, aT, kPanelB, aKP, kPanelB, 8, ID_D_KM, !first);
+      gemm_km_t<8>(tmem + C_DQU, aT, aKP, ID_D_KM, !first);
       mma_commit(&bar_mma);
     }
     ph_ku ^= 1;
     MMA_WAIT();
+    BPHASE_MARK(16);
     {  // masked dT (rows i, columns j <= i) -> slot 3 (over dSu)
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -395,29 +430,39 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       store_row32<T>(sVD, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
+    BPHASE_MARK(17);
 
     // ---- M9: X += dT @ Vu[I];  X2 = A^T @ Gb + dT^T @ Qc[I];  X3 = dZ^T @ Qu[K]
     if (tid == 0) {
       tc_fence_after();
-      gemm_km(tmem + C_X, aVD, kPanelB, aVu, kPanelB, 8, ID_D_KM, true);
-      if (!first) gemm_mm(tmem + C_X2, aA, kPanelB, aGb, kPanelB, 8, ID_D_MM, false);
-      gemm_mm(tmem + C_X2, aVD, kPanelB, aQc, kPanelB, 8, ID_D_MM, !first);
-      gemm_mm(tmem + C_X3, aT, kPanelB, aQu, kPanelB, 8, ID_D_MM, false);
+      gemm_km_t<8>(tmem + C_X, aVD, aVu, ID_D_KM, true);
+      if (!first) gemm_mm_t<8>(tmem + C_X2, aA, aGb, ID_D_MM, false);
+      gemm_mm_t<8>(tmem + C_X2, aVD, aQc, ID_D_MM, !first);
+      gemm_mm_t<8>(tmem + C_X3, aT, aQu, ID_D_MM, false);
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
-    if (cc < 3) {  // chunk groups 0,1,2: reduce dqc / dvu / dku of block I into the fp32 workspace
+    BPHASE_MARK(18);
+    if (tid == 0 && I > K) {  // every per-step input tile is dead now: prefetch the next block's Qc, Vu, Ku
+      const int in0 = (I - 1) * kBlkB;
+      mbar_expect_tx(&bar_load, 3 * OPB);
+      tma_load_4d(sQc, &m_qc, &bar_load, 0, in0, h, b);
+      tma_load_4d(sVu, &m_vu, &bar_load, 0, in0, h, b);
+      tma_load_4d(sKP, &m_ku, &bar_load, 0, in0, h, b);
+    }
+    // dqc / dvu / dku of block I: staged as fp32 panels in operand slots that are dead now and are not
+    // written again before the second phase of the next step (slot 2, Vc|dO, Wb and the spare half of
+    // slot 4), then added to the workspace by TMA reduce - whole lines at L2 instead of scattered atomics
+    uint8_t* const stage0[3] = {sT, sVD, sWb};
+    uint8_t* const stage1[3] = {sT + kPanelB, sVD + kPanelB, sKP + kPanelB};
+    if (cc < 3) {
       const uint32_t col = (cc == 0) ? C_X : (cc == 1 ? C_X2 : C_X3);
-      float* dst = ((cc == 0) ? p.acc_dqc : (cc == 1 ? p.acc_dvu : p.acc_dku)) + ((int64_t)bh * p.N + irow) * D;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         float v[32];
         tmem_ld32(trow + col + c * 32, v);
         tmem_ld_wait();
-        if (rvalid) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) red_add_v4(dst + c * 32 + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
-        }
+        store_row32_f32(c == 0 ? stage0[cc] : stage1[cc], row, v);
       }
     } else {  // chunk group 3: 16-bit copy of G including block I, for the next (lower) block
 #pragma unroll 1
@@ -429,7 +474,17 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       }
     }
     SMEM_TO_MMA_SYNC();
+    if (tid == 0) {
+      tma_reduce_add_3d(&m_acc_dqc, stage0[0], 0, i0, bh);
+      tma_reduce_add_3d(&m_acc_dqc, stage1[0], 32, i0, bh);
+      tma_reduce_add_3d(&m_acc_dvu, stage0[1], 0, i0, bh);
+      tma_reduce_add_3d(&m_acc_dvu, stage1[1], 32, i0, bh);
+      tma_reduce_add_3d(&m_acc_dku, stage0[2], 0, i0, bh);
+      tma_reduce_add_3d(&m_acc_dku, stage1[2], 32, i0, bh);
+      bulk_commit();
+    }
   }
+  if (tid == 0) bulk_wait0();
 #undef MMA_WAIT
 #undef SMEM_TO_MMA_SYNC
 
@@ -478,7 +533,8 @@ static int launch_bwd(const BwdParams& p, const CUtensorMap* maps, cudaStream_t 
   castle_bwd_delta_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
   dim3 grid(p.B * p.H, p.nblk);
   ev_start(CASTLE_KERNEL_BWD, st);
-  castle_bwd_kernel<T, D><<<grid, kBwdThreads, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6]);
+  castle_bwd_kernel<T, D><<<grid, kBwdThreads, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6],
+                                                         maps[7], maps[8], maps[9]);
   ev_stop(CASTLE_KERNEL_BWD, st);
   castle_bwd_finish_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
   e = cudaGetLastError();
@@ -530,9 +586,17 @@ extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, 
   bp.out = *out; bp.dout = *dout;
   bp.dqc = *dqc; bp.dkc = *dkc; bp.dvc = *dvc; bp.dqu = *dqu; bp.dku = *dku; bp.dvu = *dvu;
   bp.status = status;
-  CUtensorMap maps[7];
+#ifdef CASTLE_PHASE_TIMING
+  bp.timing = (long long*)((char*)workspace + need);  // the caller leaves 4 KB beyond the accumulators
+#endif
+  CUtensorMap maps[10];
   for (int i = 0; i < 7; ++i) {
     rc = make_tmap_16bit(&maps[i], ts[i], p->dtype, p->batch, p->heads, p->seq_len, p->dim_head, kBlkB, names[i]);
+    if (rc) return rc;
+  }
+  float* accs[3] = {bp.acc_dqc, bp.acc_dvu, bp.acc_dku};
+  for (int i = 0; i < 3; ++i) {
+    rc = make_tmap_f32_rows(&maps[7 + i], accs[i], p->batch * p->heads, p->seq_len, p->dim_head, "gradient workspace");
     if (rc) return rc;
   }
   cudaStream_t st = (cudaStream_t)stream;

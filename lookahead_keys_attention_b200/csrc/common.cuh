@@ -87,4 +87,18 @@ inline int make_tmap_16bit(CUtensorMap* m, const castle_tensor_t* t, int dtype, 
   return 0;
 }
 
+// Tensor map over a contiguous fp32 [BH][N][D] buffer: dims (D, N, BH), box (32, 128, 1), 128-byte swizzle.
+inline int make_tmap_f32_rows(CUtensorMap* m, float* base, int BH, int N, int D, const char* name) {
+  encode_tiled_fn fn = get_encode_fn();
+  if (!fn) return reject("cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 4, (cuuint64_t)N * D * 4};
+  cuuint32_t box[3] = {32, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return reject("%s: cuTensorMapEncodeTiled failed (CUresult %d)", name, (int)r);
+  return 0;
+}
+
 }  // namespace castle

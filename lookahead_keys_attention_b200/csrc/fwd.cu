@@ -37,11 +37,22 @@ struct FwdParams {
   int u_dtype;
   castle_tensor_t out;
   int32_t* status;
+#ifdef CASTLE_PHASE_TIMING
+  long long* timing;
+#endif
 };
 
 __host__ __device__ inline int64_t tri(int64_t i) { return i * (i + 1) / 2; }
 
 constexpr int kFwdThreads = 512;
+
+// Optional phase timing (debug builds only): thread 0 of CTA (0,0) stores clock64() at each phase
+// boundary of its first steps into the soft-max partial buffer's tail, which the host dumps.
+#ifdef CASTLE_PHASE_TIMING
+#define PHASE_MARK(i) do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && tstep < 8) p.timing[tstep * 16 + (i)] = clock64(); } while (0)
+#else
+#define PHASE_MARK(i) do { } while (0)
+#endif
 
 // 512 threads: warp w works on TMEM lanes 32*(w%4).. (the hardware's rule) and on the
 // 32-column chunk w/4 of a 128-column accumulator, so thread (row, chunk) owns 32 values.
@@ -121,6 +132,10 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   for (int I = K; I < p.nblk; ++I) {
     const int i0 = I * kBlk;
     const bool diag = (I == K);
+#ifdef CASTLE_PHASE_TIMING
+    const int tstep = I - K;
+#endif
+    PHASE_MARK(0);
     // ---- stream in Qc[I], Ku[I], Vu[I]
     if (tid == 0) {
       mbar_expect_tx(&bar_load, 3 * OPB);
@@ -133,16 +148,18 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     }
     mbar_wait(&bar_load, ph_load, abortp);
     ph_load ^= 1;
+    PHASE_MARK(1);
 
     // ---- Z[K,I] = Qu[K] @ Ku[I]^T  (rows = keys k, columns = positions j)
     if (tid == 0) {
       tc_fence_after();
-      gemm_kk(tmem + COL_S, aQu, kPanelBytes, aKuA, kPanelBytes, NP, ID_SQ, false);
+      gemm_kk_t<NP>(tmem + COL_S, aQu, aKuA, ID_SQ, false);
       mma_commit(&bar_mma);
     }
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
+    PHASE_MARK(2);
     {  // gate A = sigmoid(scale * Z), kept for j > k; written over Ku[I]
       float v[32];
       tmem_ld32(trow + COL_S + c0, v);
@@ -158,17 +175,19 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    PHASE_MARK(3);
 
     // ---- W_K += A @ Vu[I]   and   T[I,I] = Qc[I] @ Vu[I]^T
     if (tid == 0) {
       tc_fence_after();
-      gemm_km(tmem + COL_W, aKuA, kPanelBytes, aVuT, kPanelBytes, 8, ID_D, !diag);
-      gemm_kk(tmem + COL_S, aQc, kPanelBytes, aVuT, kPanelBytes, NP, ID_SQ, false);
+      gemm_km_t<8>(tmem + COL_W, aKuA, aVuT, ID_D, !diag);
+      gemm_kk_t<NP>(tmem + COL_S, aQc, aVuT, ID_SQ, false);
       mma_commit(&bar_mma);
     }
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
+    PHASE_MARK(4);
     {  // masked T (j <= i), unscaled, written over Vu[I]
       float v[32];
       tmem_ld32(trow + COL_S + c0, v);
@@ -180,17 +199,19 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    PHASE_MARK(5);
 
     // ---- Su/scale = Qc[I] @ Wb^T + Tm @ A^T   (Wb = 16-bit copy of W before this step's update)
     if (tid == 0) {
       tc_fence_after();
-      if (!diag) gemm_kk(tmem + COL_S, aQc, kPanelBytes, aWb, kPanelBytes, NP, ID_SQ, false);
-      gemm_kk(tmem + COL_S, aVuT, kPanelBytes, aKuA, kPanelBytes, 2, ID_SQ, !diag);
+      if (!diag) gemm_kk_t<NP>(tmem + COL_S, aQc, aWb, ID_SQ, false);
+      gemm_kk_t<2>(tmem + COL_S, aVuT, aKuA, ID_SQ, !diag);
       mma_commit(&bar_mma);
     }
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
+    PHASE_MARK(6);
     {  // penalty -silu(Su)/scale goes back into the accumulator; Sc is then accumulated on top of it
       float v[32];
       tmem_ld32(trow + COL_S + c0, v);
@@ -212,16 +233,18 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    PHASE_MARK(7);
 
     // ---- S/scale = penalty + Qc[I] @ Kc[K]^T
     if (tid == 0) {
       tc_fence_after();
-      gemm_kk(tmem + COL_S, aQc, kPanelBytes, aKc, kPanelBytes, NP, ID_SQ, true);
+      gemm_kk_t<NP>(tmem + COL_S, aQc, aKc, ID_SQ, true);
       mma_commit(&bar_mma);
     }
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
+    PHASE_MARK(8);
     // row max over the four column chunks, then P = exp(S - max) (rows = queries i, columns = keys k)
     const int irow = i0 + row;
     float mrow;
@@ -254,11 +277,12 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    PHASE_MARK(9);
 
     // ---- O_partial = P @ Vc[K]
     if (tid == 0) {
       tc_fence_after();
-      gemm_km(tmem + COL_O, aKuA, kPanelBytes, aVc, kPanelBytes, 8, ID_D, false);
+      gemm_km_t<8>(tmem + COL_O, aKuA, aVc, ID_D, false);
       mma_commit(&bar_mma);
     }
     const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;
@@ -270,6 +294,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
+    PHASE_MARK(10);
     if (c0 < D) {
       float* dst = p.part_o + (tile * kBlk + row) * D + c0;
       float v[32];
@@ -284,6 +309,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     fence_async_smem();  // the exchange buffer over Qc[I] was read by threads; TMA writes it next
     tc_fence_before();
     __syncthreads();
+    PHASE_MARK(11);
   }
 
   // ---- W_K is now U[K]: the cache's lookahead keys and the backward's starting state
@@ -332,6 +358,316 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   if (tid == 0 && abort_flag) atomicOr(p.status, CASTLE_STATUS_WAIT_TIMEOUT);
 }
 
+// ---------------------------------------------------------------------------------------------
+// dim_head 64: a leaner CTA (256 threads, 112 KB of shared memory, 256 TMEM columns) so that TWO
+// CTAs share an SM.  Each CTA's step is a serial chain of products and elementwise passes; with two
+// resident chains one CTA's transcendental work fills the time the other spends waiting on the
+// tensor pipe or on a barrier.  To fit, only Qu[K] stays resident: Kc[K] and Vc[K] are re-fetched by
+// TMA each step into slots that have just died (Kc over the masked T once Su is done, Vc over Qc[I]
+// once Sc is done); both fetches hide behind the elementwise pass that follows their issue.
+// Warp w owns TMEM lanes 32*(w%4).. and the 64-column half w/4 of a 128-column accumulator.
+constexpr int kFwd2Threads = 256;
+constexpr uint32_t kFwd2Smem = 7 * kPanelBytes + 256;   // 112 KB of tiles + barriers
+
+template <typename T>
+__global__ void __launch_bounds__(kFwd2Threads, 2)
+castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
+                      const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
+                      const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu) {
+  constexpr int D = 64;
+  constexpr uint32_t OPB = kPanelBytes;
+  constexpr uint32_t TM_COLS = 256;
+  constexpr uint32_t COL_W = 0, COL_S = 64, COL_O = 192;
+  constexpr int FMT = Elem<T>::fmt;
+  constexpr uint32_t ID_SQ = make_idesc(128, 128, FMT, false, false, false);
+  constexpr uint32_t ID_D = make_idesc(128, D, FMT, false, true, false);
+  constexpr float kLog2e = 1.4426950408889634f;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQu = smem;                 // resident
+  uint8_t* sQV = sQu + OPB;            // Qc[I], then Vc[K]
+  uint8_t* sWb = sQV + OPB;
+  uint8_t* sKuA = sWb + OPB;           // Ku[I] -> gate A -> P   (32 KB)
+  uint8_t* sVuT = sKuA + 2 * OPB;      // Vu[I] -> masked T (32 KB) -> Kc[K] in the first half
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sVuT + 2 * OPB);
+  uint64_t *bar_qu = bars, *bar_qc = bars + 1, *bar_ku = bars + 2, *bar_vu = bars + 3, *bar_kc = bars + 4,
+           *bar_vc = bars + 5, *bar_mma = bars + 6;
+  uint32_t* tmem_base_s = reinterpret_cast<uint32_t*>(bars + 8);
+  int* abort_flag = reinterpret_cast<int*>(bars + 9);
+  // row max / row sum exchange between the two threads of a row: over the second half of the T slot,
+  // dead from the end of the Su product until the next step's masked T is written
+  float (*red_max)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sVuT + OPB);
+  float (*red_sum)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sVuT + OPB + 2 * kBlk * sizeof(float));
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, half = warp >> 2;
+  const int row = quarter * 32 + lane;
+  const int bh = blockIdx.x, K = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int k0 = K * kBlk;
+
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
+    if (tid == 0) atomicOr(p.status, CASTLE_STATUS_BAD_LAUNCH);
+    return;
+  }
+  if (tid == 0) {
+    for (int i = 0; i < 7; ++i) mbar_init(bars + i, 1);
+    mbar_fence_init();
+    *abort_flag = 0;
+    tma_prefetch_desc(&m_qc); tma_prefetch_desc(&m_ku); tma_prefetch_desc(&m_vu);
+    tma_prefetch_desc(&m_kc); tma_prefetch_desc(&m_vc);
+  }
+  if (warp == 0) { tmem_alloc(tmem_base_s, TM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_base_s;
+  const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
+  volatile int* abortp = abort_flag;
+
+  if (tid == 0) {
+    mbar_expect_tx(bar_qu, OPB);
+    tma_load_4d(sQu, &m_qu, bar_qu, 0, k0, h, b);
+    mbar_expect_tx(bar_qc, OPB);
+    tma_load_4d(sQV, &m_qc, bar_qc, 0, k0, h, b);
+    mbar_expect_tx(bar_ku, OPB);
+    tma_load_4d(sKuA, &m_ku, bar_ku, 0, k0, h, b);
+    mbar_expect_tx(bar_vu, OPB);
+    tma_load_4d(sVuT, &m_vu, bar_vu, 0, k0, h, b);
+    mbar_wait(bar_qu, 0, abortp);
+  }
+
+  uint32_t ph_ld = 0, ph_mma = 0;   // all per-step load barriers flip once per step
+  const uint32_t aQu = smem_u32(sQu), aQV = smem_u32(sQV), aWb = smem_u32(sWb), aKuA = smem_u32(sKuA),
+                 aVuT = smem_u32(sVuT);
+  const int krow = k0 + row;
+  const float sl2 = p.scale * kLog2e;
+
+#define F2_MMA_WAIT()                   \
+  mbar_wait(bar_mma, ph_mma, abortp);   \
+  ph_mma ^= 1;                          \
+  tc_fence_after();
+#define F2_SYNC()      \
+  fence_async_smem();  \
+  tc_fence_before();   \
+  __syncthreads();
+
+  for (int I = K; I < p.nblk; ++I) {
+    const int i0 = I * kBlk;
+    const bool diag = (I == K), last = (I == p.nblk - 1);
+
+    // ---- Z[K,I] = Qu[K] @ Ku[I]^T
+    if (tid == 0) {
+      mbar_wait(bar_ku, ph_ld, abortp);
+      tc_fence_after();
+      gemm_kk_t<1>(tmem + COL_S, aQu, aKuA, ID_SQ, false);
+      mma_commit(bar_mma);
+    }
+    F2_MMA_WAIT();
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {  // gate A = sigmoid(scale * Z), kept for j > k; over Ku[I]
+      const int c0 = half * 64 + c * 32;
+      float v[32];
+      tmem_ld32(trow + COL_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = sigmoid_t<T>(v[j] * p.scale);
+      if (diag) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j > row) ? v[j] : 0.f;
+      }
+      store_row32<T>(sKuA, kPanelBytes, row, c0, v);
+    }
+    F2_SYNC();
+
+    // ---- W_K += A @ Vu[I]   and   T[I,I] = Qc[I] @ Vu[I]^T
+    if (tid == 0) {
+      mbar_wait(bar_vu, ph_ld, abortp);
+      mbar_wait(bar_qc, ph_ld, abortp);
+      tc_fence_after();
+      gemm_km_t<8>(tmem + COL_W, aKuA, aVuT, ID_D, !diag);
+      gemm_kk_t<1>(tmem + COL_S, aQV, aVuT, ID_SQ, false);
+      mma_commit(bar_mma);
+    }
+    F2_MMA_WAIT();
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {  // masked T (j <= i), unscaled; over Vu[I]
+      const int c0 = half * 64 + c * 32;
+      float v[32];
+      tmem_ld32(trow + COL_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
+      store_row32<T>(sVuT, kPanelBytes, row, c0, v);
+    }
+    F2_SYNC();
+
+    // ---- Su/scale = Qc[I] @ Wb^T + Tm @ A^T
+    if (tid == 0) {
+      tc_fence_after();
+      if (!diag) gemm_kk_t<1>(tmem + COL_S, aQV, aWb, ID_SQ, false);
+      gemm_kk_t<2>(tmem + COL_S, aVuT, aKuA, ID_SQ, !diag);
+      mma_commit(bar_mma);
+    }
+    F2_MMA_WAIT();
+    if (tid == 0) {  // the masked T is consumed: fetch Kc[K] over its first half
+      mbar_expect_tx(bar_kc, OPB);
+      tma_load_4d(sVuT, &m_kc, bar_kc, 0, k0, h, b);
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {  // penalty -silu(Su)/scale back into the accumulator
+      const int c0 = half * 64 + c * 32;
+      float v[32];
+      tmem_ld32(trow + COL_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = -v[j] * sigmoid_t<T>(v[j] * p.scale);
+      tmem_st32(trow + COL_S + c0, v);
+    }
+    {  // refresh the 16-bit copy of W (now including block I)
+      float v[32];
+      tmem_ld32(trow + COL_W + half * 32, v);
+      tmem_ld_wait();
+      store_row32<T>(sWb, kPanelBytes, row, half * 32, v);
+    }
+    tmem_st_wait();
+    F2_SYNC();
+
+    // ---- S/scale = penalty + Qc[I] @ Kc[K]^T
+    if (tid == 0) {
+      mbar_wait(bar_kc, ph_ld, abortp);
+      tc_fence_after();
+      gemm_kk_t<1>(tmem + COL_S, aQV, aVuT, ID_SQ, true);
+      mma_commit(bar_mma);
+    }
+    F2_MMA_WAIT();
+    if (tid == 0) {  // Qc[I] and Kc[K] are consumed: fetch Vc[K] over Qc, and the next Vu over Kc
+      mbar_expect_tx(bar_vc, OPB);
+      tma_load_4d(sQV, &m_vc, bar_vc, 0, k0, h, b);
+    }
+    const int irow = i0 + row;
+    float mrow, lsum = 0.f;
+    {
+      float v0[32], v1[32];
+      const int c0 = half * 64;
+      tmem_ld32(trow + COL_S + c0, v0);
+      tmem_ld32(trow + COL_S + c0 + 32, v1);
+      tmem_ld_wait();
+      if (diag) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          v0[j] = (c0 + j <= row) ? v0[j] : -INFINITY;
+          v1[j] = (c0 + 32 + j <= row) ? v1[j] : -INFINITY;
+        }
+      }
+      float mx = fmaxf(v0[0], v1[0]);
+#pragma unroll
+      for (int j = 1; j < 32; ++j) mx = fmaxf(mx, fmaxf(v0[j], v1[j]));
+      red_max[half][row] = mx;
+      __syncthreads();
+      mx = fmaxf(red_max[0][row], red_max[1][row]);
+      mrow = mx * p.scale;
+      const float mb = mx * sl2;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        v0[j] = ex2_approx(fmaf(v0[j], sl2, -mb));
+        v1[j] = ex2_approx(fmaf(v1[j], sl2, -mb));
+        lsum += v0[j] + v1[j];
+      }
+      red_sum[half][row] = lsum;
+      store_row32<T>(sKuA, kPanelBytes, row, c0, v0);
+      store_row32<T>(sKuA, kPanelBytes, row, c0 + 32, v1);
+    }
+    F2_SYNC();
+
+    // ---- O_partial = P @ Vc[K]
+    if (tid == 0) {
+      mbar_wait(bar_vc, ph_ld, abortp);
+      tc_fence_after();
+      gemm_km_t<8>(tmem + COL_O, aKuA, aQV, ID_D, false);
+      mma_commit(bar_mma);
+    }
+    const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;
+    if (half == 0 && irow < p.N) {
+      float2* ml = reinterpret_cast<float2*>(p.part_ml) + tile * kBlk + row;
+      *ml = make_float2(mrow, red_sum[0][row] + red_sum[1][row]);
+    }
+    fence_async_smem();  // the exchange buffer is read here and written by TMA (next Vu) below
+    F2_MMA_WAIT();
+    if (tid == 0 && !last) {  // every slot of this step is dead: fetch the next step's Qc, Ku, Vu
+      const int in0 = i0 + kBlk;
+      mbar_expect_tx(bar_qc, OPB);
+      tma_load_4d(sQV, &m_qc, bar_qc, 0, in0, h, b);
+      mbar_expect_tx(bar_ku, OPB);
+      tma_load_4d(sKuA, &m_ku, bar_ku, 0, in0, h, b);
+      mbar_expect_tx(bar_vu, OPB);
+      tma_load_4d(sVuT, &m_vu, bar_vu, 0, in0, h, b);
+    }
+    {
+      float* dst = p.part_o + (tile * kBlk + row) * D + half * 32;
+      float v[32];
+      tmem_ld32(trow + COL_O + half * 32, v);
+      tmem_ld_wait();
+      if (irow < p.N) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
+    }
+    ph_ld ^= 1;
+    tc_fence_before();
+    __syncthreads();
+  }
+#undef F2_MMA_WAIT
+#undef F2_SYNC
+
+  // ---- W_K is now U[K]
+  if (p.u_out.ptr != nullptr || p.w_state != nullptr) {
+    tc_fence_after();
+    const int c0 = half * 32;
+    float v[32];
+    tmem_ld32(trow + COL_W + c0, v);
+    tmem_ld_wait();
+    if (krow < p.N) {
+      if (p.w_state != nullptr) {
+        float* dst = p.w_state + ((int64_t)bh * p.N + krow) * D + c0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      }
+      if (p.u_out.ptr != nullptr) {
+        int64_t off = b * p.u_out.stride_b + h * p.u_out.stride_h + (int64_t)krow * p.u_out.stride_n + c0;
+        if (p.u_dtype == CASTLE_F32) {
+          float* dst = reinterpret_cast<float*>(p.u_out.ptr) + off;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else if (p.u_dtype == CASTLE_BF16) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.u_out.ptr) + off);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_uint4(Elem<__nv_bfloat16>::pack2(v[8 * j], v[8 * j + 1]),
+                                Elem<__nv_bfloat16>::pack2(v[8 * j + 2], v[8 * j + 3]),
+                                Elem<__nv_bfloat16>::pack2(v[8 * j + 4], v[8 * j + 5]),
+                                Elem<__nv_bfloat16>::pack2(v[8 * j + 6], v[8 * j + 7]));
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.u_out.ptr) + off);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_uint4(Elem<__half>::pack2(v[8 * j], v[8 * j + 1]),
+                                Elem<__half>::pack2(v[8 * j + 2], v[8 * j + 3]),
+                                Elem<__half>::pack2(v[8 * j + 4], v[8 * j + 5]),
+                                Elem<__half>::pack2(v[8 * j + 6], v[8 * j + 7]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TM_COLS);
+  if (tid == 0 && *abort_flag) atomicOr(p.status, CASTLE_STATUS_WAIT_TIMEOUT);
+}
+
 // Merge the per-key-block partials of one query block: out = sum_K e^{m_K - m} O_K / sum_K e^{m_K - m} l_K.
 // D/4 threads per row, each owning one float4 of the row.
 template <typename T, int D>
@@ -363,6 +699,23 @@ __global__ void __launch_bounds__(256) castle_fwd_merge_kernel(const FwdParams p
   q.y = Elem<T>::pack2(acc.z * inv, acc.w * inv);
   *reinterpret_cast<uint2*>(dst) = q;
   if (c4 == 0) p.lse[(int64_t)bh * p.N + i] = m + __logf(l);
+}
+
+template <typename T>
+static int launch_fwd_d64(const FwdParams& p, const CUtensorMap* maps, cudaStream_t st) {
+  {  // per device, so set on every call (cheap)
+    cudaError_t e = cudaFuncSetAttribute(castle_fwd_kernel_d64<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwd2Smem);
+    if (e != cudaSuccess) return cuda_fail(e, "castle_fwd attribute");
+  }
+  dim3 grid(p.B * p.H, p.nblk);
+  ev_start(CASTLE_KERNEL_FWD, st);
+  castle_fwd_kernel_d64<T><<<grid, kFwd2Threads, kFwd2Smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+  ev_stop(CASTLE_KERNEL_FWD, st);
+  constexpr int ROWS = 256 / (64 / 4);
+  dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);
+  castle_fwd_merge_kernel<T, 64><<<g2, 256, 0, st>>>(p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : cuda_fail(e, "castle_fwd launch");
 }
 
 template <typename T, int D>
@@ -436,6 +789,9 @@ extern "C" int castle_fwd(const castle_problem_t* p, const castle_tensor_t* qc, 
   fp.u_out = (u_out && u_out->ptr) ? *u_out : castle_tensor_t{nullptr, 0, 0, 0};
   fp.u_dtype = u_dtype;
   fp.out = *out; fp.status = status;
+#ifdef CASTLE_PHASE_TIMING
+  fp.timing = (long long*)((char*)workspace + need);  // the caller leaves 1 KB beyond the partials
+#endif
 
   CUtensorMap maps[6];
   for (int i = 0; i < 6; ++i) {
@@ -444,6 +800,6 @@ extern "C" int castle_fwd(const castle_problem_t* p, const castle_tensor_t* qc, 
   }
   cudaStream_t st = (cudaStream_t)stream;
   if (p->dtype == CASTLE_BF16)
-    return p->dim_head == 64 ? launch_fwd<__nv_bfloat16, 64>(fp, maps, st) : launch_fwd<__nv_bfloat16, 128>(fp, maps, st);
-  return p->dim_head == 64 ? launch_fwd<__half, 64>(fp, maps, st) : launch_fwd<__half, 128>(fp, maps, st);
+    return p->dim_head == 64 ? launch_fwd_d64<__nv_bfloat16>(fp, maps, st) : launch_fwd<__nv_bfloat16, 128>(fp, maps, st);
+  return p->dim_head == 64 ? launch_fwd_d64<__half>(fp, maps, st) : launch_fwd<__half, 128>(fp, maps, st);
 }

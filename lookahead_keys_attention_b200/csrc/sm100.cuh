@@ -72,6 +72,21 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, uint64_
       "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// 3-D tile reduce-add from shared to global memory (fp32 atomic adds at L2, whole lines at a time);
+// rows of the tile that fall outside the tensor are dropped.  Joins the thread's bulk async-group.
+__device__ __forceinline__ void tma_reduce_add_3d(const void* tmap, const void* src, int c0, int c1, int c2) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const void* tmap, const void* src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -243,6 +258,12 @@ __device__ __forceinline__ void store_row32(uint8_t* tile, uint32_t panel_bytes,
     *reinterpret_cast<uint4*>(panel + swz_off(row, chunk0 + c)) = q;
   }
 }
+// fp32 staging panel [128 rows][32 floats] with the same 128-byte swizzle: one row of 32 values
+__device__ __forceinline__ void store_row32_f32(uint8_t* panel, uint32_t row, const float* v) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<float4*>(panel + swz_off(row, c)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+}
 template <typename T>
 __device__ __forceinline__ void load_row32(const uint8_t* tile, uint32_t panel_bytes, uint32_t row, uint32_t c0,
                                            float* v) {
@@ -258,41 +279,76 @@ __device__ __forceinline__ void load_row32(const uint8_t* tile, uint32_t panel_b
 }
 
 // ---------------------------------------------------------------- whole-tile MMA helpers (one issuing thread)
-// C[128 x N] (+)= X[128 x Kc] * Y[N x Kc]^T, both operands read along rows; Kc = 64*npanels.
-__device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
-                                        uint32_t y_panel_bytes, int npanels, uint32_t idesc, bool accum) {
-  for (int p = 0; p < npanels; ++p) {
+// The issuing thread is a serial bottleneck (every product of a phase goes through it), so the
+// step counts are compile-time, the loops are unrolled and each step's descriptor is the base
+// descriptor plus a constant in its 16-byte-granular address field.
+//
+// C[128 x N] (+)= X[128 x Kc] * Y[N x Kc]^T, both operands read along rows; Kc = 64*NPANELS.
+template <int NPANELS>
+__device__ __forceinline__ void gemm_kk_t(uint32_t d_tmem, uint32_t x_addr, uint32_t y_addr, uint32_t idesc, bool accum) {
+  const uint64_t dx = desc_kmajor(x_addr), dy = desc_kmajor(y_addr);
+#pragma unroll
+  for (int p = 0; p < NPANELS; ++p) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      mma_ss(d_tmem, desc_kmajor(x_addr + p * x_panel_bytes + 32 * k), desc_kmajor(y_addr + p * y_panel_bytes + 32 * k),
-             idesc, accum || p > 0 || k > 0);
+      const uint64_t off = (uint64_t)((p * (128 * 128) + 32 * k) >> 4);
+      mma_ss(d_tmem, dx + off, dy + off, idesc, accum || p > 0 || k > 0);
     }
   }
 }
-// C[128 x N] (+)= X[128 x Kc] * Y[Kc x N]: X read along rows, Y ([Kc rows][N], panels of 64
-// columns `y_panel_bytes` apart) read down its columns.  Kc = 16*ksteps (rows of Y).
-__device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
-                                        uint32_t y_panel_bytes, int ksteps, uint32_t idesc, bool accum) {
-  for (int k = 0; k < ksteps; ++k) {
-    uint32_t xa = x_addr + (k >> 2) * x_panel_bytes + 32 * (k & 3);
-    mma_ss(d_tmem, desc_kmajor(xa), desc_mnmajor(y_addr + 2048 * k, y_panel_bytes), idesc, accum || k > 0);
+// C[128 x N] (+)= X[128 x Kc] * Y[Kc x N]: X read along rows, Y ([Kc rows][N], 64-column panels
+// 16 KB apart) read down its columns.  Kc = 16*KSTEPS (rows of Y).
+template <int KSTEPS>
+__device__ __forceinline__ void gemm_km_t(uint32_t d_tmem, uint32_t x_addr, uint32_t y_addr, uint32_t idesc, bool accum) {
+  const uint64_t dx = desc_kmajor(x_addr), dy = desc_mnmajor(y_addr, 128 * 128);
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) {
+    const uint64_t xo = (uint64_t)(((k >> 2) * (128 * 128) + 32 * (k & 3)) >> 4);
+    mma_ss(d_tmem, dx + xo, dy + (uint64_t)((2048 * k) >> 4), idesc, accum || k > 0);
   }
 }
 // C[128 x N] (+)= X^T * Y with X [Kc rows][128] and Y [Kc rows][N], both read down their columns.
-__device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
-                                        uint32_t y_panel_bytes, int ksteps, uint32_t idesc, bool accum) {
-  for (int k = 0; k < ksteps; ++k) {
-    mma_ss(d_tmem, desc_mnmajor(x_addr + 2048 * k, x_panel_bytes), desc_mnmajor(y_addr + 2048 * k, y_panel_bytes),
-           idesc, accum || k > 0);
+template <int KSTEPS>
+__device__ __forceinline__ void gemm_mm_t(uint32_t d_tmem, uint32_t x_addr, uint32_t y_addr, uint32_t idesc, bool accum) {
+  const uint64_t dx = desc_mnmajor(x_addr, 128 * 128), dy = desc_mnmajor(y_addr, 128 * 128);
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) {
+    const uint64_t off = (uint64_t)((2048 * k) >> 4);
+    mma_ss(d_tmem, dx + off, dy + off, idesc, accum || k > 0);
   }
 }
 // C[128 x N] (+)= X^T * Y^T with X [Kc rows][128] read down its columns and Y [N rows][Kc] read along rows.
+template <int KSTEPS>
+__device__ __forceinline__ void gemm_mk_t(uint32_t d_tmem, uint32_t x_addr, uint32_t y_addr, uint32_t idesc, bool accum) {
+  const uint64_t dx = desc_mnmajor(x_addr, 128 * 128), dy = desc_kmajor(y_addr);
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) {
+    const uint64_t yo = (uint64_t)(((k >> 2) * (128 * 128) + 32 * (k & 3)) >> 4);
+    mma_ss(d_tmem, dx + (uint64_t)((2048 * k) >> 4), dy + yo, idesc, accum || k > 0);
+  }
+}
+
+// Run-time-count forms (used by the self test).
+__device__ __forceinline__ void gemm_kk(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
+                                        uint32_t y_panel_bytes, int npanels, uint32_t idesc, bool accum) {
+  (void)x_panel_bytes; (void)y_panel_bytes;
+  if (npanels == 1) gemm_kk_t<1>(d_tmem, x_addr, y_addr, idesc, accum);
+  else gemm_kk_t<2>(d_tmem, x_addr, y_addr, idesc, accum);
+}
+__device__ __forceinline__ void gemm_km(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
+                                        uint32_t y_panel_bytes, int ksteps, uint32_t idesc, bool accum) {
+  (void)x_panel_bytes; (void)y_panel_bytes; (void)ksteps;
+  gemm_km_t<8>(d_tmem, x_addr, y_addr, idesc, accum);
+}
+__device__ __forceinline__ void gemm_mm(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
+                                        uint32_t y_panel_bytes, int ksteps, uint32_t idesc, bool accum) {
+  (void)x_panel_bytes; (void)y_panel_bytes; (void)ksteps;
+  gemm_mm_t<8>(d_tmem, x_addr, y_addr, idesc, accum);
+}
 __device__ __forceinline__ void gemm_mk(uint32_t d_tmem, uint32_t x_addr, uint32_t x_panel_bytes, uint32_t y_addr,
                                         uint32_t y_panel_bytes, int ksteps, uint32_t idesc, bool accum) {
-  for (int k = 0; k < ksteps; ++k) {
-    uint32_t ya = y_addr + (k >> 2) * y_panel_bytes + 32 * (k & 3);
-    mma_ss(d_tmem, desc_mnmajor(x_addr + 2048 * k, x_panel_bytes), desc_kmajor(ya), idesc, accum || k > 0);
-  }
+  (void)x_panel_bytes; (void)y_panel_bytes; (void)ksteps;
+  gemm_mk_t<8>(d_tmem, x_addr, y_addr, idesc, accum);
 }
 
 }  // namespace castle
