@@ -425,11 +425,20 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
+      BPHASE_MARK(24);
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
       store_row32<T>(sVD, kPanelB, row, c0, v);
+      BPHASE_MARK(25);
     }
+#ifdef CASTLE_PHASE_TIMING
+    fence_async_smem();
+    BPHASE_MARK(26);
+    tc_fence_before();
+    __syncthreads();
+#else
     SMEM_TO_MMA_SYNC();
+#endif
     BPHASE_MARK(17);
 
     // ---- M9: X += dT @ Vu[I];  X2 = A^T @ Gb + dT^T @ Qc[I];  X3 = dZ^T @ Qu[K]
