@@ -230,29 +230,58 @@ def run_ours(args):
             if b == shard.b0:
                 group = grp
 
-    def e2e_step():
-        x = x_host.to(dev, non_blocking=True).requires_grad_()
-        gg = g_host.to(dev, non_blocking=True)
-        for p_ in layer.parameters():
-            p_.grad = None
-        out = layer(x)
-        out.backward(gg)
-        dx, o = x.grad, out.detach()
-        if group is not None:
-            import torch.distributed as dist
-            dist.all_reduce(o, group=group)
-            dist.all_reduce(dx, group=group)
-        out_host.copy_(o, non_blocking=True)
-        dx_host.copy_(dx, non_blocking=True)
+    # Host copies run on their own streams, double-buffered: the H2D copy of step s+1 and the D2H
+    # copy of step s-1 overlap the compute of step s.  Every step still copies its own inputs in
+    # from pinned host memory and its results (out, dx) back, inside the timed region.
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    main = torch.cuda.current_stream(dev)
+    dbuf = [(torch.empty_like(x_host, device=dev), torch.empty_like(g_host, device=dev)) for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_done = torch.cuda.Event()
+
+    def prefetch(slot):
+        s_in.wait_event(ev_free[slot])
+        with torch.cuda.stream(s_in):
+            dbuf[slot][0].copy_(x_host, non_blocking=True)
+            dbuf[slot][1].copy_(g_host, non_blocking=True)
+            ev_in[slot].record(s_in)
+
+    def e2e_run(n):
+        for e in ev_free:
+            e.record(main)
+        prefetch(0)
+        for s_ in range(n):
+            slot = s_ % 2
+            if s_ + 1 < n:
+                prefetch((s_ + 1) % 2)
+            main.wait_event(ev_in[slot])
+            x = dbuf[slot][0].detach().requires_grad_()
+            for p_ in layer.parameters():
+                p_.grad = None
+            out = layer(x)
+            out.backward(dbuf[slot][1])
+            dx, o = x.grad, out.detach()
+            if group is not None:
+                import torch.distributed as dist
+                dist.all_reduce(o, group=group)
+                dist.all_reduce(dx, group=group)
+            ev_free[slot].record(main)
+            ev_done.record(main)
+            s_out.wait_event(ev_done)
+            with torch.cuda.stream(s_out):
+                out_host.copy_(o, non_blocking=True)
+                dx_host.copy_(dx, non_blocking=True)
+            o.record_stream(s_out)
+            dx.record_stream(s_out)
+        main.wait_stream(s_out)
 
     if not args.no_e2e:
-        for _ in range(args.warmup):
-            e2e_step()
+        e2e_run(args.warmup)
     barrier(world)
     e0.record()
     if not args.no_e2e:
-        for _ in range(args.steps):
-            e2e_step()
+        e2e_run(args.steps)
     e1.record()
     barrier(world)
     check_status()
