@@ -448,6 +448,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline (profiling runs)")
     ap.add_argument("--batch", type=int, default=None, help="override B (smaller case of the same workload, for ncu)")
     ap.add_argument("--seq-len", type=int, default=None, help="override N (for ncu captures)")
+    ap.add_argument("--heads", type=int, default=None, help="override H (other configurations of the same layer)")
+    ap.add_argument("--dim-head", type=int, default=None, help="override d_head (64 or 128)")
+    ap.add_argument("--dim", type=int, default=None, help="override the model width")
     ap.add_argument("--decode-steps", type=int, default=None, help="override the number of decode steps (for ncu)")
     ap.add_argument("--decode-batch", type=int, default=None, help="override the decode batch (for ncu)")
     args = ap.parse_args()
@@ -455,6 +458,12 @@ def main():
         CFG["batch"] = args.batch
     if args.seq_len:
         CFG["seq_len"] = args.seq_len
+    if args.heads:
+        CFG["heads"] = args.heads
+    if args.dim_head:
+        CFG["dim_head"] = args.dim_head
+    if args.dim:
+        CFG["dim"] = args.dim
     if args.decode_steps:
         DECODE_CFG["steps"] = args.decode_steps
     if args.decode_batch:

@@ -14,7 +14,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libcastle_b200.so"
-SOURCES = ["api.cu", "decode.cu", "selftest.cu", "fwd.cu", "bwd.cu"]
+SOURCES = ["api.cu", "decode.cu", "selftest.cu", "fwd.cu", "bwd.cu", "bwd128.cu"]
 
 BF16, F16, F32 = 0, 1, 2
 

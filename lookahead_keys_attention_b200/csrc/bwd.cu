@@ -19,77 +19,9 @@
 // Shared memory (224 KB) is time-shared: the 128x128 16-bit operands the
 // threads produce (gate A, masked T, P, dS, dSu, dZ, dT) rotate through four
 // 32 KB slots, two of which overlay input tiles that are dead by then.
-#include "common.cuh"
-#include "sm100.cuh"
+#include "bwd_common.cuh"
 
 namespace castle {
-
-constexpr int kBlkB = 128;
-constexpr uint32_t kPanelB = kBlkB * 128;
-
-struct BwdParams {
-  int B, H, N, nblk;
-  float scale;
-  const float* lse;      // [BH][N]
-  const float* w_state;  // [BH][N][D]
-  float* delta;          // [BH][N]
-  float* acc_dqc;        // [BH][N][D] fp32, zeroed
-  float* acc_dvu;
-  float* acc_dku;
-  castle_tensor_t out, dout;
-  castle_tensor_t dqc, dkc, dvc, dqu, dku, dvu;
-  int32_t* status;
-#ifdef CASTLE_PHASE_TIMING
-  long long* timing;
-#endif
-};
-
-// delta[b,h,i] = sum_d out * dout  (lookahead_keys_attention_triton.py:175-214 in the reference)
-template <typename T, int D>
-__global__ void castle_bwd_delta_kernel(const BwdParams p) {
-  constexpr int LPR = D / 8;
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / LPR) + threadIdx.x / LPR;
-  const int sub = threadIdx.x % LPR;
-  const int64_t total = (int64_t)p.B * p.H * p.N;
-  float s = 0.f;
-  if (row < total) {
-    int bh = row / p.N, i = row % p.N, b = bh / p.H, h = bh % p.H;
-    const T* po = reinterpret_cast<const T*>(p.out.ptr) + b * p.out.stride_b + h * p.out.stride_h + (int64_t)i * p.out.stride_n + sub * 8;
-    const T* pd = reinterpret_cast<const T*>(p.dout.ptr) + b * p.dout.stride_b + h * p.dout.stride_h + (int64_t)i * p.dout.stride_n + sub * 8;
-    uint4 a = *reinterpret_cast<const uint4*>(po), c = *reinterpret_cast<const uint4*>(pd);
-    const uint32_t* ua = &a.x; const uint32_t* uc = &c.x;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 x = Elem<T>::unpack2(ua[j]), y = Elem<T>::unpack2(uc[j]);
-      s += x.x * y.x + x.y * y.y;
-    }
-  }
-#pragma unroll
-  for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (row < total && sub == 0) p.delta[row] = s;
-}
-
-// fp32 accumulators -> scaled 16-bit gradients in the caller's (strided) tensors
-template <typename T, int D>
-__global__ void castle_bwd_finish_kernel(const BwdParams p) {
-  constexpr int LPR = D / 8;
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / LPR) + threadIdx.x / LPR;
-  const int sub = threadIdx.x % LPR;
-  if (row >= (int64_t)p.B * p.H * p.N) return;
-  int bh = row / p.N, i = row % p.N, b = bh / p.H, h = bh % p.H;
-  const float* srcs[3] = {p.acc_dqc, p.acc_dvu, p.acc_dku};
-  const castle_tensor_t* dsts[3] = {&p.dqc, &p.dvu, &p.dku};
-#pragma unroll
-  for (int t = 0; t < 3; ++t) {
-    const float4* s4 = reinterpret_cast<const float4*>(srcs[t] + row * D + sub * 8);
-    float4 x = s4[0], y = s4[1];
-    uint4 q;
-    q.x = Elem<T>::pack2(x.x * p.scale, x.y * p.scale); q.y = Elem<T>::pack2(x.z * p.scale, x.w * p.scale);
-    q.z = Elem<T>::pack2(y.x * p.scale, y.y * p.scale); q.w = Elem<T>::pack2(y.z * p.scale, y.w * p.scale);
-    T* d = reinterpret_cast<T*>(dsts[t]->ptr) + b * dsts[t]->stride_b + h * dsts[t]->stride_h + (int64_t)i * dsts[t]->stride_n + sub * 8;
-    *reinterpret_cast<uint4*>(d) = q;
-  }
-}
 
 constexpr int kBwdThreads = 512;
 
@@ -545,7 +477,7 @@ static int launch_bwd(const BwdParams& p, const CUtensorMap* maps, cudaStream_t 
   castle_bwd_kernel<T, D><<<grid, kBwdThreads, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6],
                                                          maps[7], maps[8], maps[9]);
   ev_stop(CASTLE_KERNEL_BWD, st);
-  castle_bwd_finish_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
+  castle_bwd_finish_kernel<T, D, 3><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : cuda_fail(e, "castle_bwd launch");
 }
@@ -557,7 +489,8 @@ using namespace castle;
 extern "C" size_t castle_bwd_workspace_bytes(const castle_problem_t* p) {
   if (!p || p->seq_len <= 0) return 0;
   int64_t rows = (int64_t)p->batch * p->heads * p->seq_len;
-  return (size_t)(rows * (3 * p->dim_head + 1) * sizeof(float));
+  int nacc = p->dim_head == 128 ? 4 : 3;
+  return (size_t)(rows * (nacc * p->dim_head + 1) * sizeof(float));
 }
 
 extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
@@ -569,7 +502,7 @@ extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, 
                           size_t workspace_bytes, int32_t* status, void* stream) {
   if (!p) return reject("castle_bwd: null problem");
   if (p->batch <= 0 || p->heads <= 0 || p->seq_len <= 0) return reject("castle_bwd: empty problem");
-  if (p->dim_head != 64) return reject("castle_bwd: dim_head %d not supported (64)", p->dim_head);
+  if (p->dim_head != 64 && p->dim_head != 128) return reject("castle_bwd: dim_head %d not supported (64 or 128)", p->dim_head);
   if (p->dtype != CASTLE_BF16 && p->dtype != CASTLE_F16) return reject("castle_bwd: dtype %d not supported (bf16, fp16)", p->dtype);
   int nblk = (p->seq_len + kBlkB - 1) / kBlkB;
   if (nblk > 65535) return reject("castle_bwd: sequence too long");
@@ -591,7 +524,8 @@ extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, 
   bp.acc_dqc = (float*)workspace;
   bp.acc_dvu = bp.acc_dqc + rows * p->dim_head;
   bp.acc_dku = bp.acc_dvu + rows * p->dim_head;
-  bp.delta = bp.acc_dku + rows * p->dim_head;
+  bp.acc_dqu = bp.acc_dku + rows * p->dim_head;                       // dim_head 128 only
+  bp.delta = (p->dim_head == 128 ? bp.acc_dqu : bp.acc_dku) + rows * p->dim_head;
   bp.out = *out; bp.dout = *dout;
   bp.dqc = *dqc; bp.dkc = *dkc; bp.dvc = *dvc; bp.dqu = *dqu; bp.dku = *dku; bp.dvu = *dvu;
   bp.status = status;
@@ -609,6 +543,7 @@ extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, 
     if (rc) return rc;
   }
   cudaStream_t st = (cudaStream_t)stream;
+  if (p->dim_head == 128) return launch_bwd128(bp, p->dtype, maps, st);
   if (p->dtype == CASTLE_BF16) return launch_bwd<__nv_bfloat16, 64>(bp, maps, st);
   return launch_bwd<__half, 64>(bp, maps, st);
 }

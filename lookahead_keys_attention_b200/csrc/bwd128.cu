@@ -1,0 +1,667 @@
+// CASTLE parallel backward for dim_head 128.
+//
+// At d = 128 the five per-key-block accumulators of the d = 64 kernel (W, G, dkc, dvc, dqu) would
+// need 640 TMEM columns, and seven 32 KB operand tiles already fill shared memory.  The pass is
+// therefore split into two kernels, each walking the query blocks I downwards for one key block
+// K and recomputing the scores (Z, gate, peeled state W, T, Su, Sc) the way the d = 64 kernel does:
+//
+//   castle_bwd128_kv_kernel   TMEM: W | dkc | dvc | scratch.  Accumulates dkc, dvc in TMEM; builds
+//                             dqc[I] = dS@Kc + dSu@Wb + dT@Vu in the scratch and adds it to the
+//                             fp32 workspace with a TMA reduce.
+//   castle_bwd128_la_kernel   TMEM: W | G | scratch | scratch.  Carries the reverse state G and
+//                             reduces dvu[I], dku[I] and dqu[K] per step.
+//
+// Shared memory is seven 32 KB slots that are re-used as tiles die; each comment "-> sN" below
+// says which slot a tile lands in.  512 threads: warp w owns TMEM lanes 32*(w%4).. and columns
+// 32*(w/4).. of every 128-column accumulator.
+#include "bwd_common.cuh"
+
+namespace castle {
+
+constexpr int kB128Threads = 512;
+constexpr uint32_t kSlot = 2 * kPanelB;                      // 32 KB
+constexpr size_t kB128Smem = 7 * kSlot + 1024;
+
+#define B128_MMA_WAIT()                  \
+  mbar_wait(&bar_mma, ph_mma, abortp);   \
+  ph_mma ^= 1;                           \
+  tc_fence_after();
+#define B128_SYNC()    \
+  fence_async_smem();  \
+  tc_fence_before();   \
+  __syncthreads();
+
+template <int NP>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* m, uint64_t* bar, int r0, int h, int b) {
+#pragma unroll
+  for (int pn = 0; pn < NP; ++pn) tma_load_4d(dst + pn * kPanelB, m, bar, pn * 64, r0, h, b);
+}
+
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kB128Threads, 1)
+castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
+                        const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
+                        const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu,
+                        const __grid_constant__ CUtensorMap m_do, const __grid_constant__ CUtensorMap m_acc_dqc) {
+  constexpr int D = 128;
+  constexpr int FMT = Elem<T>::fmt;
+  constexpr uint32_t ID_KK = make_idesc(128, 128, FMT, false, false, false);
+  constexpr uint32_t ID_KM = make_idesc(128, 128, FMT, false, true, false);
+  constexpr uint32_t ID_KM_NEG = make_idesc(128, 128, FMT, false, true, true);
+  constexpr uint32_t ID_MM = make_idesc(128, 128, FMT, true, true, false);
+  constexpr float kLog2e = 1.4426950408889634f;
+  constexpr uint32_t C_W = 0, C_DKC = 128, C_DVC = 256, C_S = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* s0 = smem;              // Qu[K] -> Wb
+  uint8_t* s1 = s0 + kSlot;        // Ku[I] -> gate A -> dT
+  uint8_t* s2 = s1 + kSlot;        // Vu[I] -> masked T -> P -> Vu[I] again
+  uint8_t* s3 = s2 + kSlot;        // Qc[I]
+  uint8_t* s4 = s3 + kSlot;        // Kc[K]
+  uint8_t* s5 = s4 + kSlot;        // Vc[K] -> dS -> dqc staging
+  uint8_t* s6 = s5 + kSlot;        // dO[I] -> dSu -> dqc staging
+  __shared__ uint64_t bar_a, bar_b, bar_vu2, bar_mma;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, cc = warp >> 2;
+  const int row = quarter * 32 + lane, c0 = cc * 32;
+  const int bh = blockIdx.x, K = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int k0 = K * kBlkB, krow = k0 + row;
+
+  if (tid == 0) {
+    mbar_init(&bar_a, 1); mbar_init(&bar_b, 1); mbar_init(&bar_vu2, 1); mbar_init(&bar_mma, 1);
+    mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
+  volatile int* abortp = &abort_flag;
+
+  if (tid == 0) {
+    const int il = (p.nblk - 1) * kBlkB;
+    mbar_expect_tx(&bar_a, 5 * kSlot);
+    load_tile<2>(s0, &m_qu, &bar_a, k0, h, b);
+    load_tile<2>(s1, &m_ku, &bar_a, il, h, b);
+    load_tile<2>(s2, &m_vu, &bar_a, il, h, b);
+    load_tile<2>(s3, &m_qc, &bar_a, il, h, b);
+    load_tile<2>(s4, &m_kc, &bar_a, k0, h, b);
+  }
+  {  // W_K starts as the forward's final state
+    const float* src = p.w_state + ((int64_t)bh * p.N + krow) * D + c0;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      float4 q = (krow < p.N) ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
+    }
+    tmem_st32(trow + C_W + c0, v);
+    tmem_st_wait();
+  }
+  tc_fence_before();
+  __syncthreads();
+
+  uint32_t ph_a = 0, ph_b = 0, ph_vu2 = 0, ph_mma = 0;
+  const uint32_t a0 = smem_u32(s0), a1 = smem_u32(s1), a2 = smem_u32(s2), a3 = smem_u32(s3), a4 = smem_u32(s4),
+                 a5 = smem_u32(s5), a6 = smem_u32(s6);
+  const float sl2 = p.scale * kLog2e;
+
+  for (int I = p.nblk - 1; I >= K; --I) {
+    const int i0 = I * kBlkB, irow = i0 + row;
+    const bool diag = (I == K), first = (I == p.nblk - 1);
+    const bool rvalid = irow < p.N;
+    const float lse_b = rvalid ? p.lse[(int64_t)bh * p.N + irow] * kLog2e : 0.f;
+    const float delta_i = rvalid ? p.delta[(int64_t)bh * p.N + irow] : 0.f;
+
+    // ---- M0: Z = Qu[K] @ Ku[I]^T
+    if (tid == 0) {
+      mbar_wait(&bar_a, ph_a, abortp);
+      tc_fence_after();
+      gemm_kk_t<2>(tmem + C_S, a0, a1, ID_KK, false);
+      mma_commit(&bar_mma);
+    }
+    ph_a ^= 1;
+    B128_MMA_WAIT();
+    {  // gate A -> s1 (over Ku)
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = sigmoid_t<T>(v[j] * p.scale);
+      if (diag) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j > row) ? v[j] : 0.f;
+      }
+      store_row32<T>(s1, kPanelB, row, c0, v);
+    }
+    B128_SYNC();
+
+    // ---- M1: peel W -= A @ Vu[I];  T = Qc[I] @ Vu[I]^T
+    if (tid == 0) {
+      tc_fence_after();
+      bulk_wait_read0();  // the dqc staging of the step before (s5, s6) has been read
+      mbar_expect_tx(&bar_b, 2 * kSlot);
+      load_tile<2>(s5, &m_vc, &bar_b, k0, h, b);
+      load_tile<2>(s6, &m_do, &bar_b, i0, h, b);
+      gemm_km_t<8>(tmem + C_W, a1, a2, ID_KM_NEG, true);
+      gemm_kk_t<2>(tmem + C_S, a3, a2, ID_KK, false);
+      mma_commit(&bar_mma);
+    }
+    B128_MMA_WAIT();
+    {  // masked T -> s2 (over Vu); 16-bit copy of the peeled state -> s0 (over Qu)
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
+      store_row32<T>(s2, kPanelB, row, c0, v);
+      tmem_ld32(trow + C_W + c0, v);
+      tmem_ld_wait();
+      store_row32<T>(s0, kPanelB, row, c0, v);
+    }
+    B128_SYNC();
+
+    // ---- M2: Su/scale = Qc[I] @ Wb^T + Tm @ A^T
+    if (tid == 0) {
+      tc_fence_after();
+      if (!diag) gemm_kk_t<2>(tmem + C_S, a3, a0, ID_KK, false);
+      gemm_kk_t<2>(tmem + C_S, a2, a1, ID_KK, !diag);
+      mma_commit(&bar_mma);
+    }
+    B128_MMA_WAIT();
+    uint32_t dpk[16], ppk[16];
+    {
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float su0 = v[j] * p.scale, su1 = v[j + 1] * p.scale;
+        float g0 = sigmoid_t<T>(su0), g1 = sigmoid_t<T>(su1);
+        v[j] = -v[j] * g0;
+        v[j + 1] = -v[j + 1] * g1;
+        dpk[j / 2] = Elem<T>::pack2(g0 * (1.f + su0 * (1.f - g0)), g1 * (1.f + su1 * (1.f - g1)));
+      }
+      tmem_st32(trow + C_S + c0, v);
+      tmem_st_wait();
+    }
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- M3: S/scale = penalty + Qc[I] @ Kc[K]^T
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_kk_t<2>(tmem + C_S, a3, a4, ID_KK, true);
+      mma_commit(&bar_mma);
+    }
+    B128_MMA_WAIT();
+    {  // P -> s2 (over the masked T)
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = ex2_approx(fmaf(v[j], sl2, -lse_b));
+      if (diag) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
+      }
+      if (!rvalid) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) ppk[j / 2] = Elem<T>::pack2(v[j], v[j + 1]);
+      store_row32<T>(s2, kPanelB, row, c0, v);
+    }
+    B128_SYNC();
+
+    // ---- M4: dvc += P^T @ dO[I];  dP = dO[I] @ Vc[K]^T
+    if (tid == 0) {
+      mbar_wait(&bar_b, ph_b, abortp);
+      tc_fence_after();
+      gemm_mm_t<8>(tmem + C_DVC, a2, a6, ID_MM, !first);
+      gemm_kk_t<2>(tmem + C_S, a6, a5, ID_KK, false);
+      mma_commit(&bar_mma);
+    }
+    ph_b ^= 1;
+    B128_MMA_WAIT();
+    if (tid == 0) {  // P is consumed: Vu[I] comes back into s2 for the last product
+      mbar_expect_tx(&bar_vu2, kSlot);
+      load_tile<2>(s2, &m_vu, &bar_vu2, i0, h, b);
+    }
+    {  // dS -> s5 (over Vc), dSu -> s6 (over dO)
+      float v[32], w[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float2 pp = Elem<T>::unpack2(ppk[j / 2]);
+        float2 dd = Elem<T>::unpack2(dpk[j / 2]);
+        float ds0 = pp.x * (v[j] - delta_i), ds1 = pp.y * (v[j + 1] - delta_i);
+        v[j] = ds0; v[j + 1] = ds1;
+        w[j] = -ds0 * dd.x; w[j + 1] = -ds1 * dd.y;
+      }
+      store_row32<T>(s5, kPanelB, row, c0, v);
+      store_row32<T>(s6, kPanelB, row, c0, w);
+    }
+    B128_SYNC();
+
+    // ---- M5: dkc += dS^T @ Qc[I];  dT = dSu @ A
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_mm_t<8>(tmem + C_DKC, a5, a3, ID_MM, !first);
+      gemm_km_t<8>(tmem + C_S, a6, a1, ID_KM, false);
+      mma_commit(&bar_mma);
+    }
+    B128_MMA_WAIT();
+    {  // masked dT -> s1 (over the gate)
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
+      store_row32<T>(s1, kPanelB, row, c0, v);
+    }
+    B128_SYNC();
+
+    // ---- M6: dqc[I] (unscaled) = dS @ Kc[K] + dSu @ Wb + dT @ Vu[I]
+    if (tid == 0) {
+      mbar_wait(&bar_vu2, ph_vu2, abortp);
+      tc_fence_after();
+      gemm_km_t<8>(tmem + C_S, a5, a4, ID_KM, false);
+      if (!diag) gemm_km_t<8>(tmem + C_S, a6, a0, ID_KM, true);
+      gemm_km_t<8>(tmem + C_S, a1, a2, ID_KM, true);
+      mma_commit(&bar_mma);
+    }
+    ph_vu2 ^= 1;
+    B128_MMA_WAIT();
+    if (tid == 0 && I > K) {  // s0..s4 are dead: prefetch the next block's tiles
+      const int in0 = (I - 1) * kBlkB;
+      mbar_expect_tx(&bar_a, 5 * kSlot);
+      load_tile<2>(s0, &m_qu, &bar_a, k0, h, b);
+      load_tile<2>(s1, &m_ku, &bar_a, in0, h, b);
+      load_tile<2>(s2, &m_vu, &bar_a, in0, h, b);
+      load_tile<2>(s3, &m_qc, &bar_a, in0, h, b);
+      load_tile<2>(s4, &m_kc, &bar_a, k0, h, b);
+    }
+    {  // stage dqc[I] as four fp32 panels over s5|s6 and add it to the workspace by TMA reduce
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+      store_row32_f32(s5 + cc * kPanelB, row, v);
+    }
+    B128_SYNC();
+    if (tid == 0) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tma_reduce_add_3d(&m_acc_dqc, s5 + c * kPanelB, c * 32, i0, bh);
+      bulk_commit();
+    }
+  }
+  if (tid == 0) bulk_wait0();
+
+  // ---- dkc (x scale) and dvc of the key block
+  {
+    tc_fence_after();
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const castle_tensor_t& dt = t == 0 ? p.dkc : p.dvc;
+      const float mul = t == 0 ? p.scale : 1.f;
+      T* dst = reinterpret_cast<T*>(dt.ptr) + b * dt.stride_b + h * dt.stride_h + (int64_t)krow * dt.stride_n + c0;
+      float v[32];
+      tmem_ld32(trow + (t == 0 ? C_DKC : C_DVC) + c0, v);
+      tmem_ld_wait();
+      if (krow < p.N) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 q;
+          q.x = Elem<T>::pack2(v[8 * j] * mul, v[8 * j + 1] * mul);
+          q.y = Elem<T>::pack2(v[8 * j + 2] * mul, v[8 * j + 3] * mul);
+          q.z = Elem<T>::pack2(v[8 * j + 4] * mul, v[8 * j + 5] * mul);
+          q.w = Elem<T>::pack2(v[8 * j + 6] * mul, v[8 * j + 7] * mul);
+          *reinterpret_cast<uint4*>(dst + j * 8) = q;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+  if (tid == 0 && abort_flag) atomicOr(p.status, CASTLE_STATUS_WAIT_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kB128Threads, 1)
+castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
+                        const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
+                        const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu,
+                        const __grid_constant__ CUtensorMap m_do, const __grid_constant__ CUtensorMap m_acc_dvu,
+                        const __grid_constant__ CUtensorMap m_acc_dku, const __grid_constant__ CUtensorMap m_acc_dqu) {
+  constexpr int D = 128;
+  constexpr int FMT = Elem<T>::fmt;
+  constexpr uint32_t ID_KK = make_idesc(128, 128, FMT, false, false, false);
+  constexpr uint32_t ID_KM = make_idesc(128, 128, FMT, false, true, false);
+  constexpr uint32_t ID_KM_NEG = make_idesc(128, 128, FMT, false, true, true);
+  constexpr uint32_t ID_MM = make_idesc(128, 128, FMT, true, true, false);
+  constexpr float kLog2e = 1.4426950408889634f;
+  constexpr uint32_t C_W = 0, C_G = 128, C_S = 256, C_X = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sG = smem;              // 16-bit copy of G (kept across steps)
+  uint8_t* sA = sG + kSlot;        // Ku[I] -> gate A -> Qu[K]
+  uint8_t* s0 = sA + kSlot;        // Qu[K] -> Kc[K] -> dT -> dqu staging
+  uint8_t* s1 = s0 + kSlot;        // Vu[I] -> dvu / dku staging
+  uint8_t* s2 = s1 + kSlot;        // Qc[I] -> dvu / dku staging
+  uint8_t* s3 = s2 + kSlot;        // dO[I] -> masked T -> dZ
+  uint8_t* s4 = s3 + kSlot;        // Vc[K] -> Wb -> dSu -> Ku[I] -> dqu staging
+  __shared__ uint64_t bar_a, bar_kc, bar_ku2, bar_qu2, bar_mma;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, cc = warp >> 2;
+  const int row = quarter * 32 + lane, c0 = cc * 32;
+  const int bh = blockIdx.x, K = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int k0 = K * kBlkB, krow = k0 + row;
+
+  if (tid == 0) {
+    mbar_init(&bar_a, 1); mbar_init(&bar_kc, 1); mbar_init(&bar_ku2, 1); mbar_init(&bar_qu2, 1); mbar_init(&bar_mma, 1);
+    mbar_fence_init();
+    abort_flag = 0;
+  }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
+  volatile int* abortp = &abort_flag;
+
+  {  // W_K starts as the forward's final state
+    const float* src = p.w_state + ((int64_t)bh * p.N + krow) * D + c0;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      float4 q = (krow < p.N) ? *reinterpret_cast<const float4*>(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
+    }
+    tmem_st32(trow + C_W + c0, v);
+    tmem_st_wait();
+  }
+  tc_fence_before();
+  __syncthreads();
+
+  uint32_t ph_a = 0, ph_kc = 0, ph_ku2 = 0, ph_qu2 = 0, ph_mma = 0;
+  const uint32_t aG = smem_u32(sG), aA = smem_u32(sA), a0 = smem_u32(s0), a1 = smem_u32(s1), a2 = smem_u32(s2),
+                 a3 = smem_u32(s3), a4 = smem_u32(s4);
+  const float sl2 = p.scale * kLog2e;
+
+  for (int I = p.nblk - 1; I >= K; --I) {
+    const int i0 = I * kBlkB, irow = i0 + row;
+    const bool diag = (I == K), first = (I == p.nblk - 1);
+    const bool rvalid = irow < p.N;
+    if (tid == 0) {
+      bulk_wait_read0();  // the staging tiles of the step before have been read by the reduces
+      mbar_expect_tx(&bar_a, 6 * kSlot);
+      load_tile<2>(s0, &m_qu, &bar_a, k0, h, b);
+      load_tile<2>(sA, &m_ku, &bar_a, i0, h, b);
+      load_tile<2>(s1, &m_vu, &bar_a, i0, h, b);
+      load_tile<2>(s2, &m_qc, &bar_a, i0, h, b);
+      load_tile<2>(s3, &m_do, &bar_a, i0, h, b);
+      load_tile<2>(s4, &m_vc, &bar_a, k0, h, b);
+    }
+    const float lse_b = rvalid ? p.lse[(int64_t)bh * p.N + irow] * kLog2e : 0.f;
+    const float delta_i = rvalid ? p.delta[(int64_t)bh * p.N + irow] : 0.f;
+
+    // ---- M0: Z = Qu[K] @ Ku[I]^T;  dP = dO[I] @ Vc[K]^T
+    if (tid == 0) {
+      mbar_wait(&bar_a, ph_a, abortp);
+      tc_fence_after();
+      gemm_kk_t<2>(tmem + C_S, a0, aA, ID_KK, false);
+      gemm_kk_t<2>(tmem + C_X, a3, a4, ID_KK, false);
+      mma_commit(&bar_mma);
+    }
+    ph_a ^= 1;
+    B128_MMA_WAIT();
+    if (tid == 0) {  // Qu is consumed: Kc[K] -> s0
+      mbar_expect_tx(&bar_kc, kSlot);
+      load_tile<2>(s0, &m_kc, &bar_kc, k0, h, b);
+    }
+    float dpv[32];  // dP of this thread's 32 entries, kept until dS is formed
+    {
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld32(trow + C_X + c0, dpv);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = sigmoid_t<T>(v[j] * p.scale);
+      if (diag) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (c0 + j > row) ? v[j] : 0.f;
+      }
+      store_row32<T>(sA, kPanelB, row, c0, v);  // gate A (over Ku)
+    }
+    B128_SYNC();
+
+    // ---- M1: peel W -= A @ Vu[I];  T = Qc[I] @ Vu[I]^T
+    if (tid == 0) {
+      tc_fence_after();
+      gemm_km_t<8>(tmem + C_W, aA, a1, ID_KM_NEG, true);
+      gemm_kk_t<2>(tmem + C_S, a2, a1, ID_KK, false);
+      mma_commit(&bar_mma);
+    }
+    B128_MMA_WAIT();
+    {  // masked T -> s3 (over dO); 16-bit copy of the peeled state -> s4 (over Vc)
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
+      store_row32<T>(s3, kPanelB, row, c0, v);
+      tmem_ld32(trow + C_W + c0, v);
+      tmem_ld_wait();
+      store_row32<T>(s4, kPanelB, row, c0, v);
+    }
+    B128_SYNC();
+
+    // ---- M2: Su/scale = Qc[I] @ Wb^T + Tm @ A^T
+    if (tid == 0) {
+      tc_fence_after();
+      if (!diag) gemm_kk_t<2>(tmem + C_S, a2, a4, ID_KK, false);
+      gemm_kk_t<2>(tmem + C_S, a3, aA, ID_KK, !diag);
+      mma_commit(&bar_mma);
+    }
+    B128_MMA_WAIT();
+    uint32_t dpk[16];
+    {
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float su0 = v[j] * p.scale, su1 = v[j + 1] * p.scale;
+        float g0 = sigmoid_t<T>(su0), g1 = sigmoid_t<T>(su1);
+        v[j] = -v[j] * g0;
+        v[j + 1] = -v[j + 1] * g1;
+        dpk[j / 2] = Elem<T>::pack2(g0 * (1.f + su0 * (1.f - g0)), g1 * (1.f + su1 * (1.f - g1)));
+      }
+      tmem_st32(trow + C_S + c0, v);
+      tmem_st_wait();
+    }
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- M3: S/scale = penalty + Qc[I] @ Kc[K]^T
+    if (tid == 0) {
+      mbar_wait(&bar_kc, ph_kc, abortp);
+      tc_fence_after();
+      gemm_kk_t<2>(tmem + C_S, a2, a0, ID_KK, true);
+      mma_commit(&bar_mma);
+    }
+    ph_kc ^= 1;
+    B128_MMA_WAIT();
+    {  // P, dS = P (dP - delta), dSu = -dS silu'(Su) -> s4 (over Wb)
+      float v[32];
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float2 dd = Elem<T>::unpack2(dpk[j / 2]);
+        bool ok0 = rvalid && (!diag || (c0 + j <= row)), ok1 = rvalid && (!diag || (c0 + j + 1 <= row));
+        float p0 = ok0 ? ex2_approx(fmaf(v[j], sl2, -lse_b)) : 0.f;
+        float p1 = ok1 ? ex2_approx(fmaf(v[j + 1], sl2, -lse_b)) : 0.f;
+        // P is rounded to the operand type first, as in the kernel that multiplies with it
+        float2 pr = Elem<T>::unpack2(Elem<T>::pack2(p0, p1));
+        v[j] = -(pr.x * (dpv[j] - delta_i)) * dd.x;
+        v[j + 1] = -(pr.y * (dpv[j + 1] - delta_i)) * dd.y;
+      }
+      store_row32<T>(s4, kPanelB, row, c0, v);
+    }
+    B128_SYNC();
+
+    // ---- M4: dA/scale = Gb @ Vu[I]^T + dSu^T @ Tm;  G += dSu^T @ Qc[I];  dT = dSu @ A
+    if (tid == 0) {
+      tc_fence_after();
+      if (!first) gemm_kk_t<2>(tmem + C_S, aG, a1, ID_KK, false);
+      gemm_mm_t<8>(tmem + C_S, a4, a3, ID_MM, !first);
+      gemm_mm_t<8>(tmem + C_G, a4, a2, ID_MM, !first);
+      gemm_km_t<8>(tmem + C_X, a4, aA, ID_KM, false);
+      mma_commit(&bar_mma);
+    }
+    B128_MMA_WAIT();
+    if (tid == 0) {  // dSu is consumed: Ku[I] -> s4 for the dqu product
+      mbar_expect_tx(&bar_ku2, kSlot);
+      load_tile<2>(s4, &m_ku, &bar_ku2, i0, h, b);
+    }
+    {  // dZ = dA A (1 - A) -> s3 (over the masked T); masked dT -> s0 (over Kc)
+      float v[32], a[32];
+      tmem_ld32(trow + C_S + c0, v);
+      load_row32<T>(sA, kPanelB, row, c0, a);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = v[j] * p.scale * a[j] * (1.f - a[j]);
+      store_row32<T>(s3, kPanelB, row, c0, v);
+      tmem_ld32(trow + C_X + c0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
+      store_row32<T>(s0, kPanelB, row, c0, v);
+    }
+    B128_SYNC();
+
+    // ---- M5: dvu[I] (unscaled) = A^T @ Gb + dT^T @ Qc[I];  dqu[K] part = dZ @ Ku[I]
+    if (tid == 0) {
+      tc_fence_after();
+      if (!first) gemm_mm_t<8>(tmem + C_X, aA, aG, ID_MM, false);
+      gemm_mm_t<8>(tmem + C_X, a0, a2, ID_MM, !first);
+      mbar_wait(&bar_ku2, ph_ku2, abortp);
+      gemm_km_t<8>(tmem + C_S, a3, a4, ID_KM, false);
+      mma_commit(&bar_mma);
+    }
+    ph_ku2 ^= 1;
+    B128_MMA_WAIT();
+    if (tid == 0) {  // the gate is consumed: Qu[K] -> sA for the dku product
+      mbar_expect_tx(&bar_qu2, kSlot);
+      load_tile<2>(sA, &m_qu, &bar_qu2, k0, h, b);
+    }
+    {  // stage dvu[I] over s1|s2 and the dqu part over s0|s4 (two fp32 panels each)
+      float v[32];
+      tmem_ld32(trow + C_X + c0, v);
+      tmem_ld_wait();
+      store_row32_f32((cc < 2 ? s1 : s2) + (cc & 1) * kPanelB, row, v);
+      tmem_ld32(trow + C_S + c0, v);
+      tmem_ld_wait();
+      store_row32_f32((cc < 2 ? s0 : s4) + (cc & 1) * kPanelB, row, v);
+    }
+    B128_SYNC();
+    if (tid == 0) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tma_reduce_add_3d(&m_acc_dvu, (c < 2 ? s1 : s2) + (c & 1) * kPanelB, c * 32, i0, bh);
+        tma_reduce_add_3d(&m_acc_dqu, (c < 2 ? s0 : s4) + (c & 1) * kPanelB, c * 32, k0, bh);
+      }
+      bulk_commit();
+    }
+
+    // ---- M6: dku[I] (unscaled) = dZ^T @ Qu[K]
+    if (tid == 0) {
+      mbar_wait(&bar_qu2, ph_qu2, abortp);
+      tc_fence_after();
+      gemm_mm_t<8>(tmem + C_X, a3, aA, ID_MM, false);
+      mma_commit(&bar_mma);
+      bulk_wait_read0();  // dvu staging (s1|s2) is free again
+    }
+    ph_qu2 ^= 1;
+    B128_MMA_WAIT();
+    __syncthreads();  // orders thread 0's wait on the reduce before everybody's staging stores
+    {
+      float v[32];
+      tmem_ld32(trow + C_X + c0, v);
+      tmem_ld_wait();
+      store_row32_f32((cc < 2 ? s1 : s2) + (cc & 1) * kPanelB, row, v);
+      // 16-bit copy of G including block I, for the next (lower) block
+      tmem_ld32(trow + C_G + c0, v);
+      tmem_ld_wait();
+      store_row32<T>(sG, kPanelB, row, c0, v);
+    }
+    B128_SYNC();
+    if (tid == 0) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tma_reduce_add_3d(&m_acc_dku, (c < 2 ? s1 : s2) + (c & 1) * kPanelB, c * 32, i0, bh);
+      bulk_commit();
+    }
+  }
+  if (tid == 0) bulk_wait0();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+  if (tid == 0 && abort_flag) atomicOr(p.status, CASTLE_STATUS_WAIT_TIMEOUT);
+}
+
+#undef B128_MMA_WAIT
+#undef B128_SYNC
+
+template <typename T>
+static int launch_bwd128_t(const BwdParams& p, const CUtensorMap* in, cudaStream_t st) {
+  constexpr int D = 128;
+  cudaError_t e = cudaFuncSetAttribute(castle_bwd128_kv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kB128Smem);
+  if (e != cudaSuccess) return cuda_fail(e, "castle_bwd attribute");
+  e = cudaFuncSetAttribute(castle_bwd128_la_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kB128Smem);
+  if (e != cudaSuccess) return cuda_fail(e, "castle_bwd attribute");
+  CUtensorMap acc[4];
+  float* bases[4] = {p.acc_dqc, p.acc_dvu, p.acc_dku, p.acc_dqu};
+  for (int i = 0; i < 4; ++i) {
+    int rc = make_tmap_f32_rows(&acc[i], bases[i], p.B * p.H, p.N, D, "gradient workspace");
+    if (rc) return rc;
+  }
+  const int64_t rows = (int64_t)p.B * p.H * p.N;
+  constexpr int RPB = 256 / (D / 8);
+  e = cudaMemsetAsync(p.acc_dqc, 0, (size_t)rows * D * 4 * sizeof(float), st);
+  if (e != cudaSuccess) return cuda_fail(e, "castle_bwd memset");
+  castle_bwd_delta_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
+  dim3 grid(p.B * p.H, p.nblk);
+  ev_start(CASTLE_KERNEL_BWD, st);
+  castle_bwd128_kv_kernel<T><<<grid, kB128Threads, kB128Smem, st>>>(p, in[0], in[1], in[2], in[3], in[4], in[5], in[6], acc[0]);
+  castle_bwd128_la_kernel<T><<<grid, kB128Threads, kB128Smem, st>>>(p, in[0], in[1], in[2], in[3], in[4], in[5], in[6], acc[1],
+                                                                    acc[2], acc[3]);
+  ev_stop(CASTLE_KERNEL_BWD, st);
+  castle_bwd_finish_kernel<T, D, 4><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : cuda_fail(e, "castle_bwd launch");
+}
+
+int launch_bwd128(const BwdParams& p, int dtype, const CUtensorMap* in_maps, cudaStream_t st) {
+  return dtype == CASTLE_BF16 ? launch_bwd128_t<__nv_bfloat16>(p, in_maps, st) : launch_bwd128_t<__half>(p, in_maps, st);
+}
+
+}  // namespace castle

@@ -118,24 +118,27 @@ def _grads(B, H, N, d, dtype, seed, std=PROJ_STD, want_ref16=False):
 
 
 @pytest.mark.parametrize("B,H,N,d", [(1, 1, 128, 64), (1, 1, 256, 64), (2, 2, 384, 64), (1, 2, 200, 64), (1, 1, 1, 64),
-                                     (1, 1, 129, 64), (1, 2, 40, 16), (1, 1, 77, 32), (1, 1, 1024, 64)])
+                                     (1, 1, 129, 64), (1, 2, 40, 16), (1, 1, 77, 32), (1, 1, 1024, 64),
+                                     (1, 1, 128, 128), (1, 1, 130, 128), (1, 2, 384, 128), (2, 1, 300, 128),
+                                     (1, 1, 1, 128), (1, 1, 72, 96), (1, 1, 640, 128)])
 def test_backward_matches_oracle_bf16(B, H, N, d):
     res = _grads(B, H, N, d, torch.bfloat16, seed=N + d)
     for name, (g, r) in res.items():
         _close(g, r, *BF16_TOL, name)
 
 
-@pytest.mark.parametrize("B,H,N,d", [(1, 2, 256, 64), (1, 1, 200, 32)])
+@pytest.mark.parametrize("B,H,N,d", [(1, 2, 256, 64), (1, 1, 200, 32), (1, 1, 260, 128)])
 def test_backward_matches_oracle_fp16(B, H, N, d):
     res = _grads(B, H, N, d, torch.float16, seed=N + d)
     for name, (g, r) in res.items():
         _close(g, r, 5e-3, 5e-3, name)
 
 
-def test_backward_matches_reference_golden():
+@pytest.mark.parametrize("name", ["core_n200_d64", "core_n130_d128", "core_n40_d16"])
+def test_backward_matches_reference_golden(name):
     """Gradients of the reference's own autograd (fp64, recorded) vs the kernels run with fp16 operands."""
     from lookahead_keys_attention_b200 import castle_attention
-    g = load_golden("core_n200_d64")
+    g = load_golden(name)
     (b, h, n, d), packed, gout = rebuild_core_case(g)
     pk = packed.float().cuda().requires_grad_()
     qu, ku, vu, qc, kc, vc = O.split_heads(pk, h)
