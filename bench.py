@@ -303,9 +303,9 @@ def run_ours(args):
                     "bwd_main_ms": round(bwd_ms, 4), "bwd_main_tflops": round(bwd_tflops, 2)},
         "roofline": {"kernel": "castle_bwd_kernel", "bound": "tensor", "achieved": round(bwd_tflops, 2),
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(bwd_tflops / peaks["tflops"], 4),
-                     # dram read+write bytes per launch: ncu capture of the B=2 case (1.055 GB), which grows
+                     # dram read+write bytes per launch: ncu capture of the B=2 case (1.068 GB), which grows
                      # in proportion to the (batch, head) pairs a launch processes
-                     "traffic": int(1.055e9 / 32 * bs * hs) if (N, d) == (4096, 64) else None,
+                     "traffic": int(1.068e9 / 32 * bs * hs) if (N, d) == (4096, 64) else None,
                      "peak_source": f"{peaks['source']} bf16 burst"},
         "clocks": clocks.summary(),
     }
@@ -382,7 +382,9 @@ def run_decode(args, world, rank, dev, peaks):
             "config": {"workload": f"cached decode B={c['batch']} H={c['heads']} d_head={c['dim_head']} prefix={c['prefix']} steps={steps}",
                        "per_gpu_batch": bs},
             "roofline": {"kernel": "castle_decode_kernel", "bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm"],
-                         "unit": "GB/s", "frac": round(gbs / peaks["hbm"], 4), "traffic": None,
+                         "unit": "GB/s", "frac": round(gbs / peaks["hbm"], 4),
+                         # ncu capture at B=8 (profiles/): dram read+write = 1.035 x the algorithmic bytes
+                         "traffic": int(alg_bytes * 1.035),
                          "algorithmic_bytes_per_launch": int(alg_bytes), "peak_source": peaks["source"]}}
 
 
