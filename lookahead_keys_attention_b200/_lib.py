@@ -90,8 +90,19 @@ def load():
     if _lib is not None:
         return _lib
     if not LIB_PATH.exists():
-        raise RuntimeError(f"{LIB_PATH} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
-                           "(needs nvcc); this package has no fallback path")
+        # compile on demand (one process at a time); there is no other code path to fall back to
+        import fcntl
+        with open(PKG_DIR / ".build.lock", "w") as lock:
+            fcntl.flock(lock, fcntl.LOCK_EX)
+            try:
+                if not LIB_PATH.exists():
+                    build(force=True)
+            except Exception as e:
+                raise RuntimeError(f"{LIB_PATH} is missing and could not be built ({e}); run "
+                                   "`python -c 'import __graft_entry__ as g; g.build()'` where nvcc is "
+                                   "available - this package has no fallback path") from e
+            finally:
+                fcntl.flock(lock, fcntl.LOCK_UN)
     lib = ctypes.CDLL(str(LIB_PATH))
     for name, (res, args) in _SIGNATURES.items():
         fn = getattr(lib, name)
