@@ -18,7 +18,8 @@
 //
 // Shared memory (224 KB) is time-shared: the 128x128 16-bit operands the
 // threads produce (gate A, masked T, P, dS, dSu, dZ, dT) rotate through four
-// 32 KB slots, two of which overlay input tiles that are dead by then.
+// 32 KB slots, two of which overlay input tiles that are dead by then
+// (slot 3 over Vc|dO holds dS then dT, slot 4 over Ku|spare holds P then dSu).
 #include "bwd_common.cuh"
 
 namespace castle {
@@ -278,12 +279,8 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     MMA_WAIT();
     BPHASE_MARK(10);
     ph_vd ^= 1;
-    if (tid == 0) {  // P is consumed: bring Ku[I] back for the dqu product
-      mbar_expect_tx(&bar_ku, OPB);
-      tma_load_4d(sKP, &m_ku, &bar_ku, 0, i0, h, b);
-    }
-    {  // dS = P * (dP - delta) -> slot 3 (over Vc|dO); dSu = -dS * silu'(Su) stays in registers
-      float v[32];
+    {  // dS = P * (dP - delta) -> slot 3 (over Vc|dO); dSu = -dS * silu'(Su) -> slot 4 (over P)
+      float v[32], w[32];
       tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
 #pragma unroll
@@ -292,42 +289,27 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
         float2 dd = Elem<T>::unpack2(dpk[j / 2]);
         float ds0 = pp.x * (v[j] - delta_i), ds1 = pp.y * (v[j + 1] - delta_i);
         v[j] = ds0; v[j + 1] = ds1;
-        dpk[j / 2] = Elem<T>::pack2(-ds0 * dd.x, -ds1 * dd.y);
+        w[j] = -ds0 * dd.x; w[j + 1] = -ds1 * dd.y;
       }
       store_row32<T>(sVD, kPanelB, row, c0, v);
+      store_row32<T>(sKP, kPanelB, row, c0, w);
     }
     SMEM_TO_MMA_SYNC();
     BPHASE_MARK(11);
 
-    // ---- M6: dkc += dS^T @ Qc[I];  X = dS @ Kc[K]
+    // ---- M6: dkc += dS^T @ Qc[I];  X = dS @ Kc[K] + dSu @ Wb;  dA/scale = Gb @ Vu[I]^T + dSu^T @ Tm
     if (tid == 0) {
       tc_fence_after();
       gemm_mm_t<8>(tmem + C_DKC, aVD, aQc, ID_D_MM, !first);
       gemm_km_t<8>(tmem + C_X, aVD, aKc, ID_D_KM, false);
+      if (!diag) gemm_km_t<8>(tmem + C_X, aKP, aWb, ID_D_KM, true);
+      if (!first) gemm_kk_t<1>(tmem + C_S, aGb, aVu, ID_SQ_KK, false);
+      gemm_mm_t<8>(tmem + C_S, aKP, aT, ID_SQ_MM, !first);
       mma_commit(&bar_mma);
     }
     MMA_WAIT();
     BPHASE_MARK(12);
-    {  // dSu -> slot 3
-      uint8_t* panel = sVD + (c0 >> 6) * kPanelB;
-      const uint32_t chunk0 = (c0 & 63) >> 3;
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        *reinterpret_cast<uint4*>(panel + swz_off(row, chunk0 + q)) =
-            make_uint4(dpk[q * 4], dpk[q * 4 + 1], dpk[q * 4 + 2], dpk[q * 4 + 3]);
-    }
-    SMEM_TO_MMA_SYNC();
     BPHASE_MARK(13);
-
-    // ---- M7: X += dSu @ Wb;  dA/scale = Gb @ Vu[I]^T + dSu^T @ Tm   (rows k, columns j)
-    if (tid == 0) {
-      tc_fence_after();
-      if (!diag) gemm_km_t<8>(tmem + C_X, aVD, aWb, ID_D_KM, true);
-      if (!first) gemm_kk_t<1>(tmem + C_S, aGb, aVu, ID_SQ_KK, false);
-      gemm_mm_t<8>(tmem + C_S, aVD, aT, ID_SQ_MM, !first);
-      mma_commit(&bar_mma);
-    }
-    MMA_WAIT();
     BPHASE_MARK(14);
     {  // dZ = dA * A * (1 - A) -> slot 2 (over Tm)
       float v[32], a[32];
@@ -341,19 +323,20 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     SMEM_TO_MMA_SYNC();
     BPHASE_MARK(15);
 
-    // ---- M8: G += dSu^T @ Qc[I];  dT = dSu @ A;  dqu += dZ @ Ku[I]
+    // ---- M8: G += dSu^T @ Qc[I];  dT = dSu @ A
     if (tid == 0) {
       tc_fence_after();
-      gemm_mm_t<8>(tmem + C_G, aVD, aQc, ID_D_MM, !first);
-      gemm_km_t<8>(tmem + C_S, aVD, aA, ID_SQ_KM, false);
-      mbar_wait(&bar_ku, ph_ku, abortp);
-      gemm_km_t<8>(tmem + C_DQU, aT, aKP, ID_D_KM, !first);
+      gemm_mm_t<8>(tmem + C_G, aKP, aQc, ID_D_MM, !first);
+      gemm_km_t<8>(tmem + C_S, aKP, aA, ID_SQ_KM, false);
       mma_commit(&bar_mma);
     }
-    ph_ku ^= 1;
     MMA_WAIT();
     BPHASE_MARK(16);
-    {  // masked dT (rows i, columns j <= i) -> slot 3 (over dSu)
+    if (tid == 0) {  // dSu is consumed: bring Ku[I] back into the first half of slot 4 for the dqu product
+      mbar_expect_tx(&bar_ku, OPB);
+      tma_load_4d(sKP, &m_ku, &bar_ku, 0, i0, h, b);
+    }
+    {  // masked dT (rows i, columns j <= i) -> slot 3 (over dS)
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
@@ -373,15 +356,18 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 #endif
     BPHASE_MARK(17);
 
-    // ---- M9: X += dT @ Vu[I];  X2 = A^T @ Gb + dT^T @ Qc[I];  X3 = dZ^T @ Qu[K]
+    // ---- M9: X += dT @ Vu[I];  X2 = A^T @ Gb + dT^T @ Qc[I];  X3 = dZ^T @ Qu[K];  dqu += dZ @ Ku[I]
     if (tid == 0) {
       tc_fence_after();
       gemm_km_t<8>(tmem + C_X, aVD, aVu, ID_D_KM, true);
       if (!first) gemm_mm_t<8>(tmem + C_X2, aA, aGb, ID_D_MM, false);
       gemm_mm_t<8>(tmem + C_X2, aVD, aQc, ID_D_MM, !first);
       gemm_mm_t<8>(tmem + C_X3, aT, aQu, ID_D_MM, false);
+      mbar_wait(&bar_ku, ph_ku, abortp);
+      gemm_km_t<8>(tmem + C_DQU, aT, aKP, ID_D_KM, !first);
       mma_commit(&bar_mma);
     }
+    ph_ku ^= 1;
     MMA_WAIT();
     BPHASE_MARK(18);
     if (tid == 0 && I > K) {  // every per-step input tile is dead now: prefetch the next block's Qc, Vu, Ku
