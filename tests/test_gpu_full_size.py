@@ -1,0 +1,105 @@
+"""GPU: the benchmark configurations at their full sizes.
+
+The dense oracle cannot hold a whole configuration (it materialises N x N tensors per head), so
+at full size the kernels are checked (a) against the oracle on a sampled (batch, head) pair -
+the pairs are independent, so one pair's result does not depend on the others being there -
+and (b) through size-independent properties: prefix invariance of the forward, linearity of
+the backward in the upstream gradient, and parallel == prefill + cached decode."""
+import pytest
+import torch
+
+from oracle import castle_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+PROJ_STD = 3 ** -0.5
+TOL = (2e-2, 1e-2)  # |a-b| <= 2e-2 + 1e-2 |b|
+
+
+def _close(a, b, what, tol=TOL):
+    err = (a - b).abs()
+    bound = tol[0] + tol[1] * b.abs()
+    assert bool((err <= bound).all()), f"{what}: max err {err.max().item():.3e}, worst excess {(err - bound).max().item():.3e}"
+
+
+def _packed(B, N, H, d, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(B, N, 6, H, d, device="cuda", generator=g) * PROJ_STD).bfloat16()
+
+
+@pytest.mark.parametrize("B,N,H,d,pair", [(4, 4096, 16, 64, (2, 11)), (1, 8192, 4, 128, (0, 3))])
+def test_sampled_pair_matches_oracle_at_full_size(B, N, H, d, pair):
+    """Config 2 (B=4 N=4096 H=16 d=64) in full, and a d=128 long-sequence case: forward, U and all six
+    gradients of one (batch, head) pair against the fp32 oracle on the same bf16 inputs."""
+    from lookahead_keys_attention_b200 import castle_attention_packed, check_status
+    packed = _packed(B, N, H, d, seed=N + d).requires_grad_()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    gout = torch.randn(B, H, N, d, device="cuda", generator=g).bfloat16()
+    out, U = castle_attention_packed(packed, d ** -0.5, True)
+    out.backward(gout)
+    torch.cuda.synchronize()
+    check_status()
+    b, h = pair
+    ins = [packed.detach()[b, :, i, h].float().cpu() for i in range(6)]  # qu,ku,vu,qc,kc,vc  (N, d)
+    qu, ku, vu, qc, kc, vc = ins
+    ro, rU = O.castle_parallel(qc, kc, vc, qu, ku, vu, d ** -0.5, return_U=True)
+    rg = O.castle_parallel_bwd(qc, kc, vc, qu, ku, vu, d ** -0.5, gout[b, h].float().cpu())  # dqc,dkc,dvc,dqu,dku,dvu
+    _close(out[b, h].float().cpu(), ro, "out")
+    ulp = 2.0 ** -8
+    _close(U[b, h].float().cpu(), rU, "U", (TOL[0] + 2 * ulp * rU.abs().max().item(), TOL[1]))
+    got = packed.grad[b, :, :, h].float().cpu()  # (N, 6, d)
+    ref16 = None
+    for name, slot, ref in [("dqc", 3, rg[0]), ("dkc", 4, rg[1]), ("dvc", 5, rg[2]), ("dqu", 0, rg[3]), ("dku", 1, rg[4]), ("dvu", 2, rg[5])]:
+        err = (got[:, slot] - ref).abs()
+        if bool((err <= TOL[0] + TOL[1] * ref.abs()).all()):
+            continue
+        # At N = 8192 the lookahead state reaches ~100 and its 16-bit copy alone breaks the element-wise
+        # rule - for the reference's own bf16 arithmetic even more so.  Then the bar is that arithmetic:
+        # the kernel's worst error must not exceed the CPU bf16 run's.
+        if ref16 is None:
+            i16 = [packed.detach()[b, :, i, h].cpu() for i in range(6)]
+            ref16 = O.castle_parallel_bwd(i16[3], i16[4], i16[5], i16[0], i16[1], i16[2], d ** -0.5, gout[b, h].cpu())
+        k = {"dqc": 0, "dkc": 1, "dvc": 2, "dqu": 3, "dku": 4, "dvu": 5}[name]
+        e16 = (ref16[k].float() - ref).abs().max().item()
+        assert err.max().item() <= e16, f"{name}: kernel {err.max().item():.3e} vs reference-bf16 {e16:.3e}"
+
+
+def test_prefix_invariance_and_backward_linearity_config2():
+    from lookahead_keys_attention_b200 import castle_attention_packed
+    B, N, H, d = 4, 4096, 16, 64
+    packed = _packed(B, N, H, d, seed=9)
+    full = castle_attention_packed(packed, 0.125, False)
+    half = castle_attention_packed(packed[:, :2048].contiguous(), 0.125, False)
+    assert torch.allclose(full[:, :, :2048].float(), half.float(), atol=1e-3)   # causality
+
+    def grads(gout):
+        p = packed.clone().requires_grad_()
+        castle_attention_packed(p, 0.125, False).backward(gout)
+        return p.grad.float()
+
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    g1 = torch.randn(B, H, N, d, device="cuda", generator=gen).bfloat16()
+    g2 = torch.randn(B, H, N, d, device="cuda", generator=gen).bfloat16()
+    mix = (0.5 * g1.float() - 0.25 * g2.float()).bfloat16()
+    lin = 0.5 * grads(g1) - 0.25 * grads(g2)
+    got = grads(mix)
+    # bf16 rounding of the mixed upstream gradient and of the results bounds the mismatch
+    rel = ((got - lin).norm() / lin.norm()).item()
+    assert rel < 1e-2, rel
+
+
+@torch.no_grad()
+def test_prefill_then_decode_equals_parallel_d128():
+    """Config-5 geometry on a slice: Castle(2048, 16 heads of 128), prefix 2048, then 16 cached steps."""
+    from lookahead_keys_attention_b200 import Castle, check_status
+    torch.manual_seed(0)
+    m = Castle(2048, heads=16, dim_head=128).cuda().bfloat16()
+    x = torch.randn(2, 2064, 2048, device="cuda").bfloat16()
+    ref = m(x)
+    out, cache = m(x[:, :2048], return_next_cache=True)
+    outs = [out]
+    for t in range(2048, 2064):
+        o, cache = m(x[:, t:t + 1], cache=cache)
+        outs.append(o)
+    check_status()
+    _close(torch.cat(outs, 1).float().cpu(), ref.float().cpu(), "prefill + decode vs parallel")
