@@ -116,3 +116,23 @@ def test_module_bf16_vs_fp32_oracle():
     for what, a, b in [("dW_qkv", m.to_all_qkv.weight.grad, w1.grad), ("dW_out", m.combine_heads.weight.grad, w2.grad)]:
         rel = ((a.float().cpu() - b).norm() / b.norm()).item()
         assert rel < 1e-2, f"{what}: rel-F {rel:.3e}"
+
+
+@torch.no_grad()
+@pytest.mark.parametrize("prenorm", [False, True])
+def test_module_rotary_parallel_equals_sequential_and_is_causal(prenorm):
+    """With rotary_emb=True (this package's own rotary embedding; the reference's third-party one is not
+    available to compare values against) the reference's two self-consistency properties still hold:
+    parallel == prefill + cached steps (tests/test_lookahead.py:10-64 there) and prefix invariance (:145-182)."""
+    from lookahead_keys_attention_b200 import Castle
+    torch.manual_seed(4)
+    m = Castle(64, heads=2, dim_head=32, rotary_emb=True, prenorm=prenorm).cuda()
+    x = torch.randn(2, 40, 64, device="cuda")
+    full = m(x)
+    out, cache = m(x[:, :24], return_next_cache=True)
+    outs = [out]
+    for t in range(24, 40):
+        o, cache = m(x[:, t:t + 1], cache=cache)
+        outs.append(o)
+    assert torch.allclose(torch.cat(outs, 1), full, atol=1e-3)
+    assert torch.allclose(full[:, :20], m(x[:, :20]), atol=1e-3)

@@ -93,3 +93,16 @@ def test_module_signature_and_state_dict():
     assert Cache._fields == ("U", "qu_cache", "kc_cache", "vc_cache")
     with pytest.raises(AssertionError):
         m(torch.zeros(1, 4, 32), cache=Cache(*([torch.zeros(1, 2, 3, 16)] * 4)))
+
+
+def test_rotary_offset_and_norm():
+    """This package's own rotary embedding: a rotation (norm preserving) whose `offset` shifts positions,
+    which is what makes a cached single-token step agree with the parallel pass."""
+    from lookahead_keys_attention_b200.castle import _Rotary
+    torch.manual_seed(0)
+    r = _Rotary(16)
+    t = torch.randn(2, 3, 10, 16)
+    full = r.rotate(t)
+    assert torch.allclose(full.norm(dim=-1), t.norm(dim=-1), atol=1e-5)
+    assert torch.allclose(r.rotate(t[:, :, 4:7], offset=4), full[:, :, 4:7], atol=1e-6)
+    assert torch.allclose(r.rotate(t[:, :, :1]), t[:, :, :1], atol=1e-6)  # position 0 is the identity
