@@ -136,3 +136,31 @@ def test_module_rotary_parallel_equals_sequential_and_is_causal(prenorm):
         outs.append(o)
     assert torch.allclose(torch.cat(outs, 1), full, atol=1e-3)
     assert torch.allclose(full[:, :20], m(x[:, :20]), atol=1e-3)
+
+
+@torch.no_grad()
+def test_module_cache_regrows_when_capacity_runs_out():
+    from lookahead_keys_attention_b200 import Castle
+    torch.manual_seed(5)
+    m = Castle(64, heads=2, dim_head=32, cache_headroom=2).cuda()
+    x = torch.randn(1, 20, 64, device="cuda")
+    out, cache = m(x[:, :3], return_next_cache=True)
+    outs, ptrs = [out], set()
+    for t in range(3, 20):
+        o, cache = m(x[:, t:t + 1], cache=cache)
+        outs.append(o)
+        ptrs.add(cache.U.data_ptr())
+        assert cache.U.shape[-2] == t + 1
+    assert len(ptrs) > 1  # the buffers were re-allocated at least once on the way
+    assert torch.allclose(torch.cat(outs, 1), m(x), atol=1e-3)
+
+
+def test_forward_batch_chunking_of_scratch(monkeypatch):
+    """The forward's partial-soft-max scratch is bounded by processing the batch in chunks."""
+    from lookahead_keys_attention_b200 import castle_attention_packed, ops
+    torch.manual_seed(6)
+    packed = (torch.randn(3, 300, 6, 2, 64, device="cuda") * 0.5).bfloat16()
+    ref, ref_u = castle_attention_packed(packed, 0.125, True)
+    monkeypatch.setattr(ops, "MAX_WORKSPACE_BYTES", 1)  # forces one batch row per launch
+    out, u = castle_attention_packed(packed, 0.125, True)
+    assert torch.equal(out, ref) and torch.equal(u, ref_u)
