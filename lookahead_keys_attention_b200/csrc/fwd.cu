@@ -30,7 +30,7 @@ struct FwdParams {
   int B, H, N, nblk;
   float scale;
   float* part_ml;   // [BH][ntiles][128][2]
-  float* part_o;    // [BH][ntiles][128][D]
+  void* part_o;     // [BH][ntiles][128][D] in the operand type (un-normalised P@Vc of one tile)
   float* lse;       // [BH][N]
   float* w_state;   // [BH][N][D] or null
   castle_tensor_t u_out;  // ptr may be null
@@ -296,14 +296,15 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     tc_fence_after();
     PHASE_MARK(10);
     if (c0 < D) {
-      float* dst = p.part_o + (tile * kBlk + row) * D + c0;
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.part_o) + (tile * kBlk + row) * D + c0);
       float v[32];
       tmem_ld32(trow + COL_O + c0, v);
       tmem_ld_wait();
       if (irow < p.N) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        for (int j = 0; j < 4; ++j)
+          dst[j] = make_uint4(Elem<T>::pack2(v[8 * j], v[8 * j + 1]), Elem<T>::pack2(v[8 * j + 2], v[8 * j + 3]),
+                              Elem<T>::pack2(v[8 * j + 4], v[8 * j + 5]), Elem<T>::pack2(v[8 * j + 6], v[8 * j + 7]));
       }
     }
     fence_async_smem();  // the exchange buffer over Qc[I] was read by threads; TMA writes it next
@@ -604,14 +605,15 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       tma_load_4d(sVuT, &m_vu, bar_vu, 0, in0, h, b);
     }
     {
-      float* dst = p.part_o + (tile * kBlk + row) * D + half * 32;
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.part_o) + (tile * kBlk + row) * D + half * 32);
       float v[32];
       tmem_ld32(trow + COL_O + half * 32, v);
       tmem_ld_wait();
       if (irow < p.N) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        for (int j = 0; j < 4; ++j)
+          dst[j] = make_uint4(Elem<T>::pack2(v[8 * j], v[8 * j + 1]), Elem<T>::pack2(v[8 * j + 2], v[8 * j + 3]),
+                              Elem<T>::pack2(v[8 * j + 4], v[8 * j + 5]), Elem<T>::pack2(v[8 * j + 6], v[8 * j + 7]));
       }
     }
     ph_ld ^= 1;
@@ -669,36 +671,41 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
 }
 
 // Merge the per-key-block partials of one query block: out = sum_K e^{m_K - m} O_K / sum_K e^{m_K - m} l_K.
-// D/4 threads per row, each owning one float4 of the row.
+// D/8 threads per row, each owning eight consecutive elements (one 16-byte load per partial).
 template <typename T, int D>
 __global__ void __launch_bounds__(256) castle_fwd_merge_kernel(const FwdParams p) {
-  constexpr int TPR = D / 4, ROWS = 256 / TPR;
+  constexpr int TPR = D / 8, ROWS = 256 / TPR;
   const int bh = blockIdx.y, I = blockIdx.x / (kBlk / ROWS), sub = blockIdx.x % (kBlk / ROWS);
-  const int r = sub * ROWS + threadIdx.x / TPR, c4 = threadIdx.x % TPR;
+  const int r = sub * ROWS + threadIdx.x / TPR, c8 = threadIdx.x % TPR;
   const int i = I * kBlk + r;
   if (i >= p.N) return;
   const int64_t tile0 = (int64_t)bh * tri(p.nblk) + tri(I);
   const float2* ml = reinterpret_cast<const float2*>(p.part_ml) + tile0 * kBlk + r;
   float m = -INFINITY;
   for (int K = 0; K <= I; ++K) m = fmaxf(m, ml[(int64_t)K * kBlk].x);
-  float l = 0.f;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  const float4* po = reinterpret_cast<const float4*>(p.part_o + (tile0 * kBlk + r) * D) + c4;
+  float l = 0.f, acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  const uint4* po = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.part_o) + (tile0 * kBlk + r) * D) + c8;
   for (int K = 0; K <= I; ++K) {
     float2 v = ml[(int64_t)K * kBlk];
     float w = __expf(v.x - m);
     l += v.y * w;
-    float4 o = po[(int64_t)K * kBlk * D / 4];
-    acc.x += o.x * w; acc.y += o.y * w; acc.z += o.z * w; acc.w += o.w * w;
+    uint4 o = po[(int64_t)K * kBlk * D / 8];
+    float2 a = Elem<T>::unpack2(o.x), b2 = Elem<T>::unpack2(o.y), c = Elem<T>::unpack2(o.z), d2 = Elem<T>::unpack2(o.w);
+    acc[0] += a.x * w; acc[1] += a.y * w; acc[2] += b2.x * w; acc[3] += b2.y * w;
+    acc[4] += c.x * w; acc[5] += c.y * w; acc[6] += d2.x * w; acc[7] += d2.y * w;
   }
   const float inv = 1.f / l;
   const int b = bh / p.H, h = bh % p.H;
-  T* dst = reinterpret_cast<T*>(p.out.ptr) + b * p.out.stride_b + h * p.out.stride_h + (int64_t)i * p.out.stride_n + c4 * 4;
-  uint2 q;
-  q.x = Elem<T>::pack2(acc.x * inv, acc.y * inv);
-  q.y = Elem<T>::pack2(acc.z * inv, acc.w * inv);
-  *reinterpret_cast<uint2*>(dst) = q;
-  if (c4 == 0) p.lse[(int64_t)bh * p.N + i] = m + __logf(l);
+  T* dst = reinterpret_cast<T*>(p.out.ptr) + b * p.out.stride_b + h * p.out.stride_h + (int64_t)i * p.out.stride_n + c8 * 8;
+  uint4 q;
+  q.x = Elem<T>::pack2(acc[0] * inv, acc[1] * inv);
+  q.y = Elem<T>::pack2(acc[2] * inv, acc[3] * inv);
+  q.z = Elem<T>::pack2(acc[4] * inv, acc[5] * inv);
+  q.w = Elem<T>::pack2(acc[6] * inv, acc[7] * inv);
+  *reinterpret_cast<uint4*>(dst) = q;
+  if (c8 == 0) p.lse[(int64_t)bh * p.N + i] = m + __logf(l);
 }
 
 template <typename T>
@@ -711,7 +718,7 @@ static int launch_fwd_d64(const FwdParams& p, const CUtensorMap* maps, cudaStrea
   ev_start(CASTLE_KERNEL_FWD, st);
   castle_fwd_kernel_d64<T><<<grid, kFwd2Threads, kFwd2Smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
   ev_stop(CASTLE_KERNEL_FWD, st);
-  constexpr int ROWS = 256 / (64 / 4);
+  constexpr int ROWS = 256 / (64 / 8);
   dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);
   castle_fwd_merge_kernel<T, 64><<<g2, 256, 0, st>>>(p);
   cudaError_t e = cudaGetLastError();
@@ -729,7 +736,7 @@ static int launch_fwd(const FwdParams& p, const CUtensorMap* maps, cudaStream_t 
   ev_start(CASTLE_KERNEL_FWD, st);
   castle_fwd_kernel<T, D><<<grid, kFwdThreads, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
   ev_stop(CASTLE_KERNEL_FWD, st);
-  constexpr int ROWS = 256 / (D / 4);
+  constexpr int ROWS = 256 / (D / 8);
   dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);
   castle_fwd_merge_kernel<T, D><<<g2, 256, 0, st>>>(p);
   cudaError_t e = cudaGetLastError();
@@ -754,7 +761,7 @@ extern "C" size_t castle_fwd_workspace_bytes(const castle_problem_t* p) {
   if (!p || p->seq_len <= 0) return 0;
   int64_t nb = (p->seq_len + kBlk - 1) / kBlk;
   int64_t tiles = (int64_t)p->batch * p->heads * tri(nb);
-  return (size_t)(tiles * kBlk * (2 + p->dim_head) * sizeof(float));
+  return (size_t)(tiles * kBlk * (2 * sizeof(float) + p->dim_head * 2));  // (max, sum) fp32 + a 16-bit row
 }
 
 extern "C" int castle_fwd(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
@@ -784,7 +791,7 @@ extern "C" int castle_fwd(const castle_problem_t* p, const castle_tensor_t* qc, 
   fp.scale = p->scale;
   int64_t tiles = (int64_t)p->batch * p->heads * tri(fp.nblk);
   fp.part_ml = (float*)workspace;
-  fp.part_o = fp.part_ml + tiles * kBlk * 2;
+  fp.part_o = fp.part_ml + tiles * kBlk * 2;  // 16-bit rows behind the fp32 (max, sum) pairs
   fp.lse = lse; fp.w_state = w_state;
   fp.u_out = (u_out && u_out->ptr) ? *u_out : castle_tensor_t{nullptr, 0, 0, 0};
   fp.u_dtype = u_dtype;

@@ -46,7 +46,7 @@ def test_argument_rejection_without_gpu():
     prob = L.CastleProblem(1, 1, 128, 64, L.BF16, 0.125)
     rc = lib.castle_fwd(ctypes.byref(prob), ctypes.byref(t_bad), *args[1:], None, None, 0, None, None, 0, None, None)
     assert rc < 0 and "aligned" in L.last_error()
-    assert lib.castle_fwd_workspace_bytes(ctypes.byref(prob)) == 128 * 66 * 4
+    assert lib.castle_fwd_workspace_bytes(ctypes.byref(prob)) == 128 * (8 + 64 * 2)
     assert lib.castle_bwd_workspace_bytes(ctypes.byref(prob)) == 128 * (3 * 64 + 1) * 4
 
 
