@@ -300,12 +300,14 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     // ---- M6: dkc += dS^T @ Qc[I];  X = dS @ Kc[K] + dSu @ Wb;  dA/scale = Gb @ Vu[I]^T + dSu^T @ Tm
     if (tid == 0) {
       tc_fence_after();
-      gemm_mm_t<8>(tmem + C_DKC, aVD, aQc, ID_D_MM, !first);
-      gemm_km_t<8>(tmem + C_X, aVD, aKc, ID_D_KM, false);
-      if (!diag) gemm_km_t<8>(tmem + C_X, aKP, aWb, ID_D_KM, true);
+      // dA first and committed alone: the pass that turns it into dZ only needs dA, so it overlaps the
+      // products issued after the commit (dkc, X), which the next phase's commit covers
       if (!first) gemm_kk_t<1>(tmem + C_S, aGb, aVu, ID_SQ_KK, false);
       gemm_mm_t<8>(tmem + C_S, aKP, aT, ID_SQ_MM, !first);
       mma_commit(&bar_mma);
+      gemm_mm_t<8>(tmem + C_DKC, aVD, aQc, ID_D_MM, !first);
+      gemm_km_t<8>(tmem + C_X, aVD, aKc, ID_D_KM, false);
+      if (!diag) gemm_km_t<8>(tmem + C_X, aKP, aWb, ID_D_KM, true);
     }
     MMA_WAIT();
     BPHASE_MARK(12);
@@ -328,7 +330,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       tc_fence_after();
       gemm_mm_t<8>(tmem + C_G, aKP, aQc, ID_D_MM, !first);
       gemm_km_t<8>(tmem + C_S, aKP, aA, ID_SQ_KM, false);
-      mma_commit(&bar_mma);
+      mma_commit(&bar_mma);   // covers the G update too: dSu's slot is re-loaded with Ku right after
     }
     MMA_WAIT();
     BPHASE_MARK(16);

@@ -257,9 +257,9 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     // ---- M5: dkc += dS^T @ Qc[I];  dT = dSu @ A
     if (tid == 0) {
       tc_fence_after();
-      gemm_mm_t<8>(tmem + C_DKC, a5, a3, ID_MM, !first);
       gemm_km_t<8>(tmem + C_S, a6, a1, ID_KM, false);
-      mma_commit(&bar_mma);
+      mma_commit(&bar_mma);  // dT alone: masking it overlaps the dkc product, which the next commit covers
+      gemm_mm_t<8>(tmem + C_DKC, a5, a3, ID_MM, !first);
     }
     B128_MMA_WAIT();
     {  // masked dT -> s1 (over the gate)
