@@ -21,6 +21,7 @@ struct DecodeParams {
   float* part;                                     // [BH][nsplit][2 + D]
   int H, t, nsplit, rows_per_split;
   float scale;
+  int32_t* status;
 };
 
 template <typename T> struct Vec;  // 16 bytes of T <-> floats
@@ -228,6 +229,203 @@ __global__ void __launch_bounds__(kDecodeThreads, CASTLE_DECODE_MIN_CTAS) castle
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Same step, with the four caches brought in by bulk asynchronous copies (the TMA engine) into a
+// ring of shared-memory stages instead of per-thread loads: the bytes in flight no longer depend
+// on how many warps are resident or on how many registers a thread can spare.  One thread issues,
+// per stage, four contiguous copies (the rows of a tile are adjacent in each cache, which is why
+// this variant needs position stride == dim_head); the warps consume a stage row group by row
+// group, write U back from registers, and the stage is refilled after a block-wide barrier.
+constexpr int kRingRows = 16;     // rows per stage
+constexpr int kRingStages = 3;
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kDecodeThreads, 4) castle_decode_ring_kernel(const DecodeParams p) {
+  constexpr int VEC = Vec<T>::N;
+  constexpr int LPR = D / VEC;
+  constexpr int RPW = 32 / LPR;
+  constexpr int NW = kDecodeThreads / 32;
+  constexpr int PASSES = (kRingRows + RPW * NW - 1) / (RPW * NW);
+  constexpr uint32_t ROWB = D * sizeof(T);
+  constexpr uint32_t TENB = kRingRows * ROWB;            // one tensor's tile
+  extern __shared__ __align__(128) uint8_t ring[];       // [stage][tensor: qu, U, kc, vc][row][D]
+  __shared__ uint64_t full[kRingStages];
+  __shared__ int abort_flag;
+  __shared__ float s_m[NW], s_l[NW], s_acc[NW][D];
+
+  const int bh = blockIdx.x, split = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LPR, grp = lane / LPR;
+  const int64_t col = (int64_t)sub * VEC;
+  volatile int* abortp = &abort_flag;
+
+  auto row_ptr = [&](const castle_tensor_t& t, int64_t r) {
+    return reinterpret_cast<T*>(t.ptr) + b * t.stride_b + h * t.stride_h + r * t.stride_n + col;
+  };
+  const int r_begin = split * p.rows_per_split;
+  const int r_end = min(p.t, r_begin + p.rows_per_split);
+  const int ntiles = (max(r_end - r_begin, 0) + kRingRows - 1) / kRingRows;
+
+  auto issue = [&](int tile) {  // thread 0 only
+    const int st = tile % kRingStages;
+    const int r0 = r_begin + tile * kRingRows;
+    const uint32_t bytes = (uint32_t)min(kRingRows, r_end - r0) * ROWB;
+    uint8_t* dst = ring + (size_t)st * 4 * TENB;
+    mbar_expect_tx(&full[st], 4 * bytes);
+    bulk_load(dst, row_ptr(p.quc, r0) - col, bytes, &full[st]);
+    bulk_load(dst + TENB, row_ptr(p.U, r0) - col, bytes, &full[st]);
+    bulk_load(dst + 2 * TENB, row_ptr(p.kcc, r0) - col, bytes, &full[st]);
+    bulk_load(dst + 3 * TENB, row_ptr(p.vcc, r0) - col, bytes, &full[st]);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRingStages; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+    abort_flag = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int t0 = 0; t0 < kRingStages && t0 < ntiles; ++t0) issue(t0);
+
+  float qcv[VEC], kuv[VEC], vuv[VEC];
+  Vec<T>::load(row_ptr(p.qc, 0), qcv);
+  Vec<T>::load(row_ptr(p.ku, 0), kuv);
+  Vec<T>::load(row_ptr(p.vu, 0), vuv);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) { qcv[i] *= p.scale; kuv[i] *= p.scale; }
+
+  float m = -INFINITY, l = 0.f, acc[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+
+  for (int tile = 0; tile < ntiles; ++tile) {
+    const int st = tile % kRingStages;
+    mbar_wait(&full[st], (uint32_t)((tile / kRingStages) & 1), abortp);
+    const uint8_t* src = ring + (size_t)st * 4 * TENB;
+    const int r0 = r_begin + tile * kRingRows;
+#pragma unroll
+    for (int ps = 0; ps < PASSES; ++ps) {
+      const int rr = ps * RPW * NW + warp * RPW + grp;   // row inside the tile
+      const int r = r0 + rr;
+      const bool live = rr < kRingRows && r < r_end;
+      float quv[VEC], uv[VEC], kv[VEC], vv[VEC];
+      if (live) {
+        const T* base = reinterpret_cast<const T*>(src) + (size_t)rr * D + col;
+        Vec<T>::load(base, quv);
+        Vec<T>::load(base + kRingRows * D, uv);
+        Vec<T>::load(base + 2 * kRingRows * D, kv);
+        Vec<T>::load(base + 3 * kRingRows * D, vv);
+      }
+      float z = 0.f, sc = 0.f, su = 0.f;
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) z += quv[i] * kuv[i];
+      }
+      z = group_sum<LPR>(z);
+      const float a = sigmoid_f(z);
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) uv[i] += a * vuv[i];
+        Vec<T>::round(uv);
+        Vec<T>::store(row_ptr(p.U, r), uv);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) { sc += qcv[i] * kv[i]; su += qcv[i] * uv[i]; }
+      }
+      sc = group_sum<LPR>(sc);
+      su = group_sum<LPR>(su);
+      if (live) {
+        const float s = sc - su * sigmoid_f(su);
+        const float mn = fmaxf(m, s);
+        const float corr = __expf(m - mn), pe = __expf(s - mn);
+        l = l * corr + pe;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = acc[i] * corr + pe * vv[i];
+        m = mn;
+      }
+    }
+    __syncthreads();  // every warp is done with this stage
+    if (threadIdx.x == 0 && tile + kRingStages < ntiles) issue(tile + kRingStages);
+  }
+
+  // the appended row: U[t] = 0 so its score is just qc.kc_new; done by the last split
+  if (split == p.nsplit - 1 && warp == 0) {
+    float kn[VEC], vn[VEC], qn[VEC], zero[VEC];
+    Vec<T>::load(row_ptr(p.kc, 0), kn);
+    Vec<T>::load(row_ptr(p.vc, 0), vn);
+    Vec<T>::load(row_ptr(p.qu, 0), qn);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) zero[i] = 0.f;
+    if (grp == 0) {
+      Vec<T>::store(row_ptr(p.kcc, p.t), kn);
+      Vec<T>::store(row_ptr(p.vcc, p.t), vn);
+      Vec<T>::store(row_ptr(p.quc, p.t), qn);
+      Vec<T>::store(row_ptr(p.U, p.t), zero);
+    }
+    float sc = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sc += qcv[i] * kn[i];
+    sc = group_sum<LPR>(sc);
+    if (grp == 0) {
+      const float mn = fmaxf(m, sc);
+      const float corr = __expf(m - mn), pe = __expf(sc - mn);
+      l = l * corr + pe;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = acc[i] * corr + pe * vn[i];
+      m = mn;
+    }
+  }
+
+  // merge the lane groups of a warp, then the warps of the CTA
+#pragma unroll
+  for (int o = LPR; o < 32; o <<= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), l2 = __shfl_xor_sync(0xffffffffu, l, o);
+    const float mn = fmaxf(m, m2);
+    const float c1 = (m == -INFINITY) ? 0.f : __expf(m - mn), c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+    l = l * c1 + l2 * c2;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const float a2 = __shfl_xor_sync(0xffffffffu, acc[i], o);
+      acc[i] = acc[i] * c1 + a2 * c2;
+    }
+    m = mn;
+  }
+  if (grp == 0) {
+    if (sub == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) s_acc[warp][sub * VEC + i] = acc[i];
+  }
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) mm = fmaxf(mm, s_m[w]);
+    float ll = 0.f, aa = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const float c = (s_m[w] == -INFINITY) ? 0.f : __expf(s_m[w] - mm);
+      ll += s_l[w] * c;
+      aa += s_acc[w][threadIdx.x] * c;
+    }
+    if (p.nsplit == 1) {
+      T* o = reinterpret_cast<T*>(p.out.ptr) + b * p.out.stride_b + h * p.out.stride_h;
+      if constexpr (sizeof(T) == 4) o[threadIdx.x] = aa / ll;
+      else o[threadIdx.x] = Elem<T>::from_f(aa / ll);
+    } else {
+      float* dst = p.part + ((int64_t)bh * p.nsplit + split) * (2 + D);
+      if (threadIdx.x == 0) { dst[0] = mm; dst[1] = ll; }
+      dst[2 + threadIdx.x] = aa;
+    }
+  }
+  if (threadIdx.x == 0 && abort_flag) atomicOr(p.status, CASTLE_STATUS_WAIT_TIMEOUT);
+}
+
 template <typename T, int D>
 __global__ void castle_decode_merge_kernel(const DecodeParams p) {
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H, c = threadIdx.x;
@@ -250,7 +448,7 @@ __global__ void castle_decode_merge_kernel(const DecodeParams p) {
 // CASTLE_DECODE_MIN_CTAS CTAs per SM, so what matters is that the grid fills whole "waves" of
 // resident CTAs: pick the smallest split (at least 128 rows each, at most 64) whose last wave is
 // nearly full.
-static int decode_nsplit(int BH, int t) {
+static int decode_nsplit(int BH, int t, int ctas_per_sm = CASTLE_DECODE_MIN_CTAS) {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0, n = 0;
@@ -260,7 +458,7 @@ static int decode_nsplit(int BH, int t) {
     else
       sms = 148;
   }
-  const int slots = sms * CASTLE_DECODE_MIN_CTAS;
+  const int slots = sms * ctas_per_sm;
   int max_ns = t / 128;
   if (max_ns > 64) max_ns = 64;
   if (max_ns < 1) max_ns = 1;
@@ -275,9 +473,32 @@ static int decode_nsplit(int BH, int t) {
   return best;
 }
 
+constexpr int kRingCtasPerSm = 4;
+
+// The bulk-copy variant needs rows that are adjacent in memory and at least 128 bytes long.
+static bool decode_use_ring(int D, int dtype, const castle_tensor_t* const* caches) {
+  if (kDecodeThreads != 128 || D * elem_size(dtype) < 128) return false;
+  for (int i = 0; i < 4; ++i)
+    if (caches[i]->stride_n != D) return false;
+  return true;
+}
+
 template <typename T, int D>
-static int launch_decode(const DecodeParams& p, int BH, cudaStream_t st) {
+static int launch_decode(const DecodeParams& p, int BH, bool ring, cudaStream_t st) {
   dim3 grid(BH, p.nsplit);
+  if constexpr (D * sizeof(T) >= 128) {
+    if (ring) {
+      constexpr size_t smem = (size_t)kRingStages * 4 * kRingRows * D * sizeof(T);
+      cudaError_t e = cudaFuncSetAttribute(castle_decode_ring_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return cuda_fail(e, "castle_decode_step attribute");
+      ev_start(CASTLE_KERNEL_DECODE, st);
+      castle_decode_ring_kernel<T, D><<<grid, kDecodeThreads, smem, st>>>(p);
+      ev_stop(CASTLE_KERNEL_DECODE, st);
+      if (p.nsplit > 1) castle_decode_merge_kernel<T, D><<<BH, D, 0, st>>>(p);
+      e = cudaGetLastError();
+      return e == cudaSuccess ? 0 : cuda_fail(e, "castle_decode_step launch");
+    }
+  }
   ev_start(CASTLE_KERNEL_DECODE, st);
   castle_decode_kernel<T, D><<<grid, kDecodeThreads, 0, st>>>(p);
   ev_stop(CASTLE_KERNEL_DECODE, st);
@@ -287,12 +508,12 @@ static int launch_decode(const DecodeParams& p, int BH, cudaStream_t st) {
 }
 
 template <typename T>
-static int launch_decode_d(const DecodeParams& p, int BH, int D, cudaStream_t st) {
+static int launch_decode_d(const DecodeParams& p, int BH, int D, bool ring, cudaStream_t st) {
   switch (D) {
-    case 16: return launch_decode<T, 16>(p, BH, st);
-    case 32: return launch_decode<T, 32>(p, BH, st);
-    case 64: return launch_decode<T, 64>(p, BH, st);
-    case 128: return launch_decode<T, 128>(p, BH, st);
+    case 16: return launch_decode<T, 16>(p, BH, ring, st);
+    case 32: return launch_decode<T, 32>(p, BH, ring, st);
+    case 64: return launch_decode<T, 64>(p, BH, ring, st);
+    case 128: return launch_decode<T, 128>(p, BH, ring, st);
   }
   return reject("castle_decode_step: dim_head %d not supported (16, 32, 64, 128)", D);
 }
@@ -304,7 +525,8 @@ using namespace castle;
 extern "C" size_t castle_decode_workspace_bytes(const castle_problem_t* p, int32_t cache_len) {
   if (!p) return 0;
   int BH = p->batch * p->heads;
-  return (size_t)BH * decode_nsplit(BH, cache_len) * (2 + p->dim_head) * sizeof(float);
+  int ns = decode_nsplit(BH, cache_len), ns_ring = decode_nsplit(BH, cache_len, kRingCtasPerSm);
+  return (size_t)BH * (ns > ns_ring ? ns : ns_ring) * (2 + p->dim_head) * sizeof(float);
 }
 
 extern "C" int castle_decode_step(const castle_problem_t* p, int32_t cache_len, int32_t capacity,
@@ -315,7 +537,6 @@ extern "C" int castle_decode_step(const castle_problem_t* p, int32_t cache_len, 
                                   const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache,
                                   const castle_tensor_t* out, void* workspace, size_t workspace_bytes,
                                   int32_t* status, void* stream) {
-  (void)status;
   if (!p) return reject("castle_decode_step: null problem");
   if (p->batch <= 0 || p->heads <= 0) return reject("castle_decode_step: empty batch/heads");
   if (cache_len < 0 || cache_len >= capacity)
@@ -331,8 +552,10 @@ extern "C" int castle_decode_step(const castle_problem_t* p, int32_t cache_len, 
   dp.qc = *qc_new; dp.kc = *kc_new; dp.vc = *vc_new; dp.qu = *qu_new; dp.ku = *ku_new; dp.vu = *vu_new;
   dp.U = *u_cache; dp.quc = *qu_cache; dp.kcc = *kc_cache; dp.vcc = *vc_cache; dp.out = *out;
   int BH = p->batch * p->heads;
-  dp.H = p->heads; dp.t = cache_len; dp.scale = p->scale;
-  dp.nsplit = decode_nsplit(BH, cache_len);
+  dp.H = p->heads; dp.t = cache_len; dp.scale = p->scale; dp.status = status;
+  const castle_tensor_t* caches[4] = {u_cache, qu_cache, kc_cache, vc_cache};
+  const bool ring = status != nullptr && decode_use_ring(p->dim_head, p->dtype, caches);
+  dp.nsplit = decode_nsplit(BH, cache_len, ring ? kRingCtasPerSm : CASTLE_DECODE_MIN_CTAS);
   dp.rows_per_split = (cache_len + dp.nsplit - 1) / dp.nsplit;
   if (dp.rows_per_split < 1) dp.rows_per_split = 1;
   dp.part = (float*)workspace;
@@ -343,9 +566,9 @@ extern "C" int castle_decode_step(const castle_problem_t* p, int32_t cache_len, 
   }
   cudaStream_t st = (cudaStream_t)stream;
   switch (p->dtype) {
-    case CASTLE_BF16: return launch_decode_d<__nv_bfloat16>(dp, BH, p->dim_head, st);
-    case CASTLE_F16: return launch_decode_d<__half>(dp, BH, p->dim_head, st);
-    default: return launch_decode_d<float>(dp, BH, p->dim_head, st);
+    case CASTLE_BF16: return launch_decode_d<__nv_bfloat16>(dp, BH, p->dim_head, ring, st);
+    case CASTLE_F16: return launch_decode_d<__half>(dp, BH, p->dim_head, ring, st);
+    default: return launch_decode_d<float>(dp, BH, p->dim_head, ring, st);
   }
 }
 
@@ -379,7 +602,6 @@ extern "C" int castle_decode_step_static(const castle_problem_t* p, int32_t cach
                                          const castle_tensor_t* u_cache, const castle_tensor_t* qu_cache,
                                          const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache,
                                          const castle_tensor_t* out, int32_t* status, void* stream) {
-  (void)status;
   if (!p) return reject("castle_decode_step_static: null problem");
   if (p->batch <= 0 || p->heads <= 0) return reject("castle_decode_step_static: empty batch/heads");
   if (cache_len < 0 || cache_len >= capacity)
@@ -411,7 +633,7 @@ extern "C" int castle_decode_step_static(const castle_problem_t* p, int32_t cach
   DecodeParams dp;
   dp.qc = *qc_new; dp.kc = *kc_new; dp.vc = *vc_new; dp.qu = *qu_new; dp.ku = *ku_new; dp.vu = *vu_new;
   dp.U = *u_cache; dp.quc = *qu_cache; dp.kcc = *kc_cache; dp.vcc = *vc_cache; dp.out = *out;
-  dp.H = p->heads; dp.t = cache_len; dp.scale = p->scale;
+  dp.H = p->heads; dp.t = cache_len; dp.scale = p->scale; dp.status = status;
   dp.nsplit = nsplit;
   dp.rows_per_split = (cache_len + nsplit - 1) / nsplit;
   if (dp.rows_per_split < 1) dp.rows_per_split = 1;
@@ -420,8 +642,8 @@ extern "C" int castle_decode_step_static(const castle_problem_t* p, int32_t cach
   dp.part = g_decode_static_ptr[dev];
   cudaStream_t st = (cudaStream_t)stream;
   switch (p->dtype) {
-    case CASTLE_BF16: return launch_decode_d<__nv_bfloat16>(dp, BH, p->dim_head, st);
-    case CASTLE_F16: return launch_decode_d<__half>(dp, BH, p->dim_head, st);
-    default: return launch_decode_d<float>(dp, BH, p->dim_head, st);
+    case CASTLE_BF16: return launch_decode_d<__nv_bfloat16>(dp, BH, p->dim_head, false, st);
+    case CASTLE_F16: return launch_decode_d<__half>(dp, BH, p->dim_head, false, st);
+    default: return launch_decode_d<float>(dp, BH, p->dim_head, false, st);
   }
 }
