@@ -381,10 +381,10 @@ def run_decode(args, world, rank, dev, peaks):
             "ms_per_step": round(ms, 4), "kernel_ms": round(kms, 4),
             "config": {"workload": f"cached decode B={c['batch']} H={c['heads']} d_head={c['dim_head']} prefix={c['prefix']} steps={steps}",
                        "per_gpu_batch": bs},
-            "roofline": {"kernel": "castle_decode_kernel", "bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm"],
+            "roofline": {"kernel": "castle_decode_ring_kernel", "bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm"],
                          "unit": "GB/s", "frac": round(gbs / peaks["hbm"], 4),
-                         # ncu capture at B=8 (profiles/): dram read+write = 1.035 x the algorithmic bytes
-                         "traffic": int(alg_bytes * 1.035),
+                         # ncu capture at B=8 (profiles/): dram read+write = 0.98 x the algorithmic bytes
+                         "traffic": int(alg_bytes * 0.98),
                          "algorithmic_bytes_per_launch": int(alg_bytes), "peak_source": peaks["source"]}}
 
 
