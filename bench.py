@@ -91,7 +91,7 @@ class ClockSampler:
                             self.reasons.add(name)
                 except Exception:
                     pass
-                time.sleep(0.005)
+                time.sleep(0.002)
         except Exception as e:  # NVML missing: report that, do not fail the run
             self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
 
@@ -383,7 +383,7 @@ def run_decode(args, world, rank, dev, peaks):
                        "per_gpu_batch": bs},
             "roofline": {"kernel": "castle_decode_ring_kernel", "bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm"],
                          "unit": "GB/s", "frac": round(gbs / peaks["hbm"], 4),
-                         # ncu capture at B=8 (profiles/): dram read+write = 0.98 x the algorithmic bytes
+                         # ncu capture at B=8: dram read+write = 0.98 x the algorithmic bytes
                          "traffic": int(alg_bytes * 0.98),
                          "algorithmic_bytes_per_launch": int(alg_bytes), "peak_source": peaks["source"]}}
 

@@ -90,7 +90,9 @@ def core_case(Castle, name, b, h, n, d, seed):
 
 
 if __name__ == "__main__":
-    Castle = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path to a checkout of lookahead-keys-attention>")
+    Castle = load_reference(sys.argv[1])
     # shapes of the reference's own tests (tests/test_lookahead.py:18-23, 153-157, 75-79)
     module_case(Castle, "module_d16", 32, 2, 16, False, 2, 16, 8, 0)
     module_case(Castle, "module_d16_prenorm", 32, 2, 16, True, 2, 16, 8, 1)
