@@ -105,7 +105,8 @@ int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, const castl
  * `cache_len` to all four (a zero row for U, :185-188,202) and writes the
  * attention output for the new token (:190-200).  Requires cache_len < capacity.
  * The six `*_new` tensors are the new token's (batch, heads, 1, dim_head) rows,
- * unscaled.  `workspace` holds split partials.
+ * unscaled.  `workspace` holds split partials.  Caches whose position stride equals dim_head (rows adjacent in
+ * memory, at least 128 bytes each) take the fastest path.
  */
 size_t castle_decode_workspace_bytes(const castle_problem_t* p, int32_t cache_len);
 
