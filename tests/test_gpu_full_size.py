@@ -103,3 +103,26 @@ def test_prefill_then_decode_equals_parallel_d128():
         outs.append(o)
     check_status()
     _close(torch.cat(outs, 1).float().cpu(), ref.float().cpu(), "prefill + decode vs parallel")
+
+
+def test_repeatability_config2():
+    """Nothing in the forward, and nothing in dkc / dvc / dqu, is reduced atomically: two runs on the same
+    inputs must agree bit for bit at full size (a race in a shared-memory or TMEM hand-off would show here)."""
+    from lookahead_keys_attention_b200 import castle_attention_packed, check_status
+    packed = _packed(4, 4096, 16, 64, seed=21)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    gout = torch.randn(4, 16, 4096, 64, device="cuda", generator=gen).bfloat16()
+    res = []
+    for _ in range(3):
+        p = packed.clone().requires_grad_()
+        out, U = castle_attention_packed(p, 0.125, True)
+        out.backward(gout)
+        res.append((out.detach().clone(), U.clone(), p.grad.clone()))
+    torch.cuda.synchronize()
+    check_status()
+    for out, U, g in res[1:]:
+        assert torch.equal(out, res[0][0]) and torch.equal(U, res[0][1])
+        for slot in (0, 4, 5):  # dqu, dkc, dvc
+            assert torch.equal(g[:, :, slot], res[0][2][:, :, slot])
+        # dqc, dku, dvu are fp32 sums in arrival order: equal up to a few bf16 ulps of the result
+        assert torch.allclose(g.float(), res[0][2].float(), atol=3e-2, rtol=3e-2)
