@@ -311,8 +311,6 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     }
     MMA_WAIT();
     BPHASE_MARK(12);
-    BPHASE_MARK(13);
-    BPHASE_MARK(14);
     {  // dZ = dA * A * (1 - A) -> slot 2 (over Tm)
       float v[32], a[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -323,7 +321,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       store_row32<T>(sT, kPanelB, row, c0, v);
     }
     SMEM_TO_MMA_SYNC();
-    BPHASE_MARK(15);
+    BPHASE_MARK(13);
 
     // ---- M8: G += dSu^T @ Qc[I];  dT = dSu @ A
     if (tid == 0) {
@@ -333,7 +331,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mma_commit(&bar_mma);   // covers the G update too: dSu's slot is re-loaded with Ku right after
     }
     MMA_WAIT();
-    BPHASE_MARK(16);
+    BPHASE_MARK(14);
     if (tid == 0) {  // dSu is consumed: bring Ku[I] back into the first half of slot 4 for the dqu product
       mbar_expect_tx(&bar_ku, OPB);
       tma_load_4d(sKP, &m_ku, &bar_ku, 0, i0, h, b);
@@ -342,21 +340,12 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
-      BPHASE_MARK(24);
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
       store_row32<T>(sVD, kPanelB, row, c0, v);
-      BPHASE_MARK(25);
     }
-#ifdef CASTLE_PHASE_TIMING
-    fence_async_smem();
-    BPHASE_MARK(26);
-    tc_fence_before();
-    __syncthreads();
-#else
     SMEM_TO_MMA_SYNC();
-#endif
-    BPHASE_MARK(17);
+    BPHASE_MARK(15);
 
     // ---- M9: X += dT @ Vu[I];  X2 = A^T @ Gb + dT^T @ Qc[I];  X3 = dZ^T @ Qu[K];  dqu += dZ @ Ku[I]
     if (tid == 0) {
@@ -371,7 +360,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     }
     ph_ku ^= 1;
     MMA_WAIT();
-    BPHASE_MARK(18);
+    BPHASE_MARK(16);
     if (tid == 0 && I > K) {  // every per-step input tile is dead now: prefetch the next block's Qc, Vu, Ku
       const int in0 = (I - 1) * kBlkB;
       mbar_expect_tx(&bar_load, 3 * OPB);
@@ -412,6 +401,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       tma_reduce_add_3d(&m_acc_dku, stage1[2], 32, i0, bh);
       bulk_commit();
     }
+    BPHASE_MARK(17);
   }
   if (tid == 0) bulk_wait0();
 #undef MMA_WAIT

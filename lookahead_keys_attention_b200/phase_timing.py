@@ -1,0 +1,75 @@
+"""Developer aid: per-phase cycle counts of the d=64 backward kernel.
+
+Builds a DEBUG copy of the library with -DCASTLE_PHASE_TIMING (thread 0 of CTA (0,0) stores
+clock64() at every phase boundary of its first eight tile steps behind the workspace), runs one
+forward and a few backward passes on random inputs and prints the cycles each phase took.
+
+    python -m lookahead_keys_attention_b200.phase_timing [B H N]
+
+The shipped library is built without the flag; this never touches it.
+"""
+import ctypes
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+import torch
+
+from . import _lib as L
+
+PHASES = ["wait for Qc/Vu/Ku", "MMA Z", "gate A", "MMA peel, T", "masked T, Wb", "MMA Su", "penalty, silu'",
+          "MMA Sc", "P", "MMA dvc, dP", "dS, dSu", "MMA dA (+dkc, X)", "dZ", "MMA G, dT", "masked dT",
+          "MMA X, X2, X3, dqu", "stage + issue reduce"]
+
+
+def main():
+    B, H, N = (int(a) for a in sys.argv[1:4]) if len(sys.argv) >= 4 else (4, 16, 4096)
+    d = 64
+    out = Path(tempfile.mkdtemp()) / "libcastle_timing.so"
+    srcs = [str(L.CSRC / f) for f in ("api.cu", "fwd.cu", "bwd.cu", "bwd128.cu")]
+    subprocess.run([L._nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-shared", "-Xcompiler",
+                    "-fPIC", "-DCASTLE_PHASE_TIMING", "-o", str(out)] + srcs, check=True)
+    lib = ctypes.CDLL(str(out))
+    for name in ("castle_fwd", "castle_bwd", "castle_fwd_workspace_bytes", "castle_bwd_workspace_bytes"):
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = L._SIGNATURES[name]
+    dev = "cuda"
+    packed = (torch.randn(B, N, 6, H, d, device=dev) * 3 ** -0.5).bfloat16()
+    qu, ku, vu, qc, kc, vc = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(6))
+    o = torch.empty(B, N, H, d, device=dev, dtype=torch.bfloat16).permute(0, 2, 1, 3)
+    do = torch.randn(B, N, H, d, device=dev).bfloat16().permute(0, 2, 1, 3)
+    lse = torch.empty(B, H, N, device=dev)
+    wst = torch.empty(B, H, N, d, device=dev)
+    gp = torch.empty(B, N, 6, H, d, device=dev, dtype=torch.bfloat16)
+    g = [gp[:, :, i].permute(0, 2, 1, 3) for i in range(6)]
+    prob = L.CastleProblem(B, H, N, d, L.BF16, d ** -0.5)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    desc = lambda t: L.CastleTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+    ref = lambda ts: [ctypes.byref(desc(t)) for t in ts]
+    need_f = lib.castle_fwd_workspace_bytes(ctypes.byref(prob))
+    wsf = torch.zeros(need_f + 4096, dtype=torch.uint8, device=dev)
+    keep = [desc(t) for t in (qc, kc, vc, qu, ku, vu, o)]
+    rc = lib.castle_fwd(ctypes.byref(prob), *[ctypes.byref(x) for x in keep], lse.data_ptr(), None, 0, wst.data_ptr(),
+                        wsf.data_ptr(), wsf.numel(), st.data_ptr(), None)
+    assert rc == 0, lib.castle_last_error()
+    need = lib.castle_bwd_workspace_bytes(ctypes.byref(prob))
+    ws = torch.zeros(need + 8192, dtype=torch.uint8, device=dev)
+    a = [desc(t) for t in (qc, kc, vc, qu, ku, vu, o, do)]
+    gr = [desc(t) for t in (g[3], g[4], g[5], g[0], g[1], g[2])]
+    for _ in range(3):
+        rc = lib.castle_bwd(ctypes.byref(prob), *[ctypes.byref(x) for x in a], lse.data_ptr(), wst.data_ptr(),
+                            *[ctypes.byref(x) for x in gr], ws.data_ptr(), ws.numel(), st.data_ptr(), None)
+        assert rc == 0
+    torch.cuda.synchronize()
+    t = ws[need:need + 8 * 32 * 8].view(torch.int64).cpu().view(8, 32)[1:7, :18]   # steps 1..6 of CTA (0,0)
+    dt = (t[:, 1:] - t[:, :-1]).double().mean(0)
+    print(f"castle_bwd_kernel<bf16,64>  B={B} H={H} N={N}: cycles per phase, CTA (0,0), mean of tile steps 1-6")
+    for name, c in zip(PHASES, dt.tolist()):
+        print(f"  {name:24s} {c:8.0f}")
+    mma = sum(c for n, c in zip(PHASES, dt.tolist()) if n.startswith("MMA"))
+    print(f"  {'total':24s} {dt.sum().item():8.0f}   (MMA phases {mma:.0f}, elementwise and waits {dt.sum().item() - mma:.0f})")
+
+
+if __name__ == "__main__":
+    main()
