@@ -239,6 +239,9 @@ def run_ours(args):
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_free = [torch.cuda.Event() for _ in range(2)]
     ev_done = torch.cuda.Event()
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    hold = [None, None]  # results stay referenced until their D2H copy is known to be done (no record_stream:
+    #                      it would make the caching allocator grow, and cudaMalloc, inside the timed region)
 
     def prefetch(slot):
         s_in.wait_event(ev_free[slot])
@@ -248,7 +251,7 @@ def run_ours(args):
             ev_in[slot].record(s_in)
 
     def e2e_run(n):
-        for e in ev_free:
+        for e in ev_free + ev_out:
             e.record(main)
         prefetch(0)
         for s_ in range(n):
@@ -256,6 +259,8 @@ def run_ours(args):
             if s_ + 1 < n:
                 prefetch((s_ + 1) % 2)
             main.wait_event(ev_in[slot])
+            main.wait_event(ev_out[slot])   # the copy that read hold[slot] two steps ago has finished
+            hold[slot] = None
             x = dbuf[slot][0].detach().requires_grad_()
             for p_ in layer.parameters():
                 p_.grad = None
@@ -266,15 +271,16 @@ def run_ours(args):
                 import torch.distributed as dist
                 dist.all_reduce(o, group=group)
                 dist.all_reduce(dx, group=group)
+            hold[slot] = (o, dx)
             ev_free[slot].record(main)
             ev_done.record(main)
             s_out.wait_event(ev_done)
             with torch.cuda.stream(s_out):
                 out_host.copy_(o, non_blocking=True)
                 dx_host.copy_(dx, non_blocking=True)
-            o.record_stream(s_out)
-            dx.record_stream(s_out)
+                ev_out[slot].record(s_out)
         main.wait_stream(s_out)
+        hold[0] = hold[1] = None
 
     if not args.no_e2e:
         e2e_run(args.warmup)
