@@ -85,6 +85,12 @@ MAX_WORKSPACE_BYTES = 8 << 30
 class _CastleAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U):
+        return _CastleAttention.run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U,
+                                            any(ctx.needs_input_grad[:6]))
+
+    @staticmethod
+    def run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, need_grad):
+        """Shared by the six-view and the packed operator; `need_grad` says whether to save state."""
         _require_cuda(qc, "castle_attention")
         lib = _lib.load()
         B, H, N, d = qc.shape
@@ -105,7 +111,6 @@ class _CastleAttention(torch.autograd.Function):
 
         ins = [prep(t) for t in (qc, kc, vc, qu, ku, vu)]
         dev = qc.device
-        need_grad = any(ctx.needs_input_grad[:6]) if len(ctx.needs_input_grad) > 3 else ctx.needs_input_grad[0]
         # laid out (B, N, H, d): merging heads afterwards is a free reshape
         out = torch.empty(B, N, H, dp, dtype=cdtype, device=dev).permute(0, 2, 1, 3)
         lse = torch.empty(B, H, N, dtype=torch.float32, device=dev)
@@ -179,10 +184,7 @@ class _CastleAttentionPacked(torch.autograd.Function):
     @staticmethod
     def forward(ctx, packed, scale, return_U):
         qu, ku, vu, qc, kc, vc = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(6))
-        inner = _CastleAttention
-        # run the six-view forward with this ctx standing in (it only stores tensors and scalars)
-        res = inner.forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U)
-        return res
+        return _CastleAttention.run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, ctx.needs_input_grad[0])
 
     @staticmethod
     def backward(ctx, do, dU=None):
