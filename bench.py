@@ -169,7 +169,8 @@ def run_ours(args):
     lib = _lib.load()
     peaks = load_peaks()
     B, N, H, d, dim = (CFG[k] for k in ("batch", "seq_len", "heads", "dim_head", "dim"))
-    shard = partition(B, H, world, rank)
+    weak = args.scaling == "weak"
+    shard = partition(B, H, 1, 0) if weak else partition(B, H, world, rank)
     bs, hs = shard.b1 - shard.b0, shard.h1 - shard.h0
     layer = make_layer(shard, dev)
     g = torch.Generator().manual_seed(1)
@@ -213,6 +214,8 @@ def run_ours(args):
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
     bwd_ms = sum(e[2].elapsed_time(e[3]) for e in ev) / args.steps
     f_fwd, f_bwd = core_flops(B, H, N, d)
+    if weak:
+        f_fwd, f_bwd = f_fwd * world, f_bwd * world
     value = (f_fwd + f_bwd) / (ms_core * 1e-3) / 1e12
     rank_f_fwd, rank_f_bwd = core_flops(bs, hs, N, d)
     bwd_tflops = rank_f_bwd / (bwd_ms * 1e-3) / 1e12
@@ -222,7 +225,7 @@ def run_ours(args):
     out_host = torch.empty(bs, N, dim, dtype=torch.bfloat16).pin_memory()
     dx_host = torch.empty(bs, N, dim, dtype=torch.bfloat16).pin_memory()
     group = None
-    if world > B:  # ranks that share a batch row hold different heads: their projections' outputs add up
+    if world > B and not weak:  # ranks that share a batch row hold different heads: their projections' outputs add up
         import torch.distributed as dist
         per = world // B
         for b in range(B):
@@ -297,7 +300,7 @@ def run_ours(args):
     line = {
         "metric": "castle_attn_fwd_bwd_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_core, 4), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"castle_attention_layer B={B} N={N} H={H} d_head={d} dim={dim}, forward+backward",
                    "sharding": f"batch x head rectangles, {bs}x{hs} pairs per GPU", "flops": "19*B*H*N^2*d algorithmic",
                    "l2": "inputs_exceed_l2 (q/k/v, grads and scratch of one step are > 126 MB)"},
@@ -452,6 +455,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="strong (default): the fixed B=4,H=16 problem is split over the GPUs, as the benchmark "
+                         "configuration says; weak: every GPU runs the whole problem (global batch 4*N)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end arm (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline (profiling runs)")
     ap.add_argument("--batch", type=int, default=None, help="override B (smaller case of the same workload, for ncu)")
