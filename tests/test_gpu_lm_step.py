@@ -23,6 +23,17 @@ class ByteLM(nn.Module):
         self.norm = nn.RMSNorm(dim)
         self.logits = nn.Linear(dim, 256, bias=False)
 
+    def logits_with_cache(self, ids, caches=None):
+        """Per-layer cache list, the way the reference's sampling loop threads it (train_triton.py:113-139 there)."""
+        h = self.emb(ids)
+        new = []
+        for i, (a, f) in enumerate(zip(self.attn, self.ff)):
+            o, c = a(h, cache=None if caches is None else caches[i], return_next_cache=True)
+            new.append(c)
+            h = o + h
+            h = f(h) + h
+        return self.logits(self.norm(h)), new
+
     def forward(self, ids):
         x, y = ids[:, :-1], ids[:, 1:]
         h = self.emb(x)
@@ -85,3 +96,21 @@ def test_lm_training_steps_full_size():
     check_status()
     assert all(torch.isfinite(torch.tensor(losses))) and 4.5 < losses[0] < 7.0  # ln(256) = 5.55 at init
     assert losses[-1] < losses[0], losses  # the same batch is fitted a little better each step
+
+
+@torch.no_grad()
+def test_lm_prompt_then_cached_decode_matches_teacher_forcing():
+    """Feed a prompt once (parallel pass, caches returned), then one token at a time with the per-layer cache
+    list; the logits must equal those of a single parallel pass over the whole sequence."""
+    from lookahead_keys_attention_b200 import Castle, check_status
+    torch.manual_seed(1)
+    lm = ByteLM(3, 128, 2, 64, Castle).cuda()
+    ids = torch.randint(0, 256, (2, 48), device="cuda")
+    full, _ = lm.logits_with_cache(ids)
+    logits, caches = lm.logits_with_cache(ids[:, :32])
+    outs = [logits]
+    for t in range(32, 48):
+        logits, caches = lm.logits_with_cache(ids[:, t:t + 1], caches)
+        outs.append(logits)
+    check_status()
+    assert torch.allclose(torch.cat(outs, 1), full, atol=2e-3)
