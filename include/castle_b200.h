@@ -159,6 +159,13 @@ int castle_set_kernel_events(int32_t which, void* start_event, void* stop_event)
  */
 int castle_selftest_mma(int32_t mode, const void* x, const void* y, float* d, int32_t* status, void* stream);
 
+/* Measurement aid (no counterpart in the reference): `reps` back-to-back 128 x n x 16 tensor-core
+ * products in one operand form (0: both operands read along rows, 1: B read down its columns,
+ * 2: both read down their columns, 3: A read down its columns), n in {64, 128, 192, 256}.
+ * cycles[0] = SM cycles spent issuing, cycles[1] = cycles from first issue to completion
+ * (device pointer to two int64). */
+int castle_selftest_mma_rate(int32_t form, int32_t n, int32_t reps, long long* cycles, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

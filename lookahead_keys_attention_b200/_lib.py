@@ -80,6 +80,7 @@ _SIGNATURES = {
     "castle_decode_step": (ctypes.c_int, [_PR, _i32, _i32] + [_T] * 11 + [_vp, _sz, _vp, _vp]),
     "castle_decode_step_static": (ctypes.c_int, [_PR, _i32, _i32] + [_T] * 11 + [_vp, _vp]),
     "castle_set_kernel_events": (ctypes.c_int, [_i32, _vp, _vp]),
+    "castle_selftest_mma_rate": (ctypes.c_int, [_i32, _i32, _i32, _vp, _vp, _vp]),
     "castle_selftest_mma": (ctypes.c_int, [_i32, _vp, _vp, _vp, _vp, _vp]),
 }
 

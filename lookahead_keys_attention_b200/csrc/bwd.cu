@@ -25,6 +25,7 @@
 namespace castle {
 
 constexpr int kBwdThreads = 512;
+constexpr int kPrefetchTid = 384;
 
 // Optional phase timing (debug builds only): thread 0 of CTA (0,0) stores clock64() at each phase
 // boundary of its first steps behind the fp32 workspace, which the host dumps.
@@ -36,6 +37,23 @@ constexpr int kBwdThreads = 512;
 
 // 512 threads: warp w works on TMEM lanes 32*(w%4).. and on the 32-column chunk w/4 of a
 // 128-column accumulator, so thread (row, chunk) owns 32 values of every 128x128 tile.
+// One 128 x 64 fp32 accumulator tile from tensor memory into two swizzled 128 x 32 staging panels.
+__device__ __forceinline__ void stage_f32_tile(uint32_t taddr, uint8_t* panel0, uint8_t* panel1, uint32_t row) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    float v[32];
+    tmem_ld32(taddr + c * 32, v);
+    tmem_ld_wait();
+    store_row32_f32(c == 0 ? panel0 : panel1, row, v);
+  }
+}
+// Timing experiments only (never in the shipped library): drop the reduces to see what they cost.
+#ifdef CASTLE_TIMING_SKIP_REDUCE
+#define tma_reduce_add_3d(...) do { } while (0)
+#endif
+// Barrier over the 128 threads (four warps) of one chunk group.
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
@@ -72,7 +90,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   uint8_t* sGb = sWb + OPB;
   uint8_t* sA = sGb + OPB;             // slot 1: gate A
   uint8_t* sT = sA + SQB;              // slot 2: masked T, later dZ
-  __shared__ uint64_t bar_res, bar_load, bar_vd, bar_ku, bar_mma;
+  __shared__ uint64_t bar_res, bar_load, bar_vd, bar_ku, bar_mma, bar_x1, bar_x2, bar_kn;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -86,6 +104,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 
   if (tid == 0) {
     mbar_init(&bar_res, 1); mbar_init(&bar_load, 1); mbar_init(&bar_vd, 1); mbar_init(&bar_ku, 1); mbar_init(&bar_mma, 1);
+    mbar_init(&bar_x1, 1); mbar_init(&bar_x2, 1); mbar_init(&bar_kn, 1);
     mbar_fence_init();
     abort_flag = 0;
   }
@@ -102,10 +121,11 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     tma_load_4d(sQu, &m_qu, &bar_res, 0, k0, h, b);
     tma_load_4d(sKc, &m_kc, &bar_res, 0, k0, h, b);
     // first step's Qc, Vu, Ku; later steps prefetch theirs at the end of the step before
-    mbar_expect_tx(&bar_load, 3 * OPB);
+    mbar_expect_tx(&bar_kn, OPB);
+    tma_load_4d(sKP, &m_ku, &bar_kn, 0, (p.nblk - 1) * kBlkB, h, b);
+    mbar_expect_tx(&bar_load, 2 * OPB);
     tma_load_4d(sQc, &m_qc, &bar_load, 0, (p.nblk - 1) * kBlkB, h, b);
     tma_load_4d(sVu, &m_vu, &bar_load, 0, (p.nblk - 1) * kBlkB, h, b);
-    tma_load_4d(sKP, &m_ku, &bar_load, 0, (p.nblk - 1) * kBlkB, h, b);
   }
   // W_K starts as the forward's final state
   if (c0 < D) {
@@ -123,7 +143,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   tc_fence_before();
   __syncthreads();
 
-  uint32_t ph_load = 0, ph_vd = 0, ph_ku = 0, ph_mma = 0;
+  uint32_t ph_load = 0, ph_vd = 0, ph_ku = 0, ph_mma = 0, ph_x = 0;
   const uint32_t aQu = smem_u32(sQu), aKc = smem_u32(sKc), aQc = smem_u32(sQc), aVu = smem_u32(sVu),
                  aVc = smem_u32(sVc), adO = smem_u32(sdO), aKP = smem_u32(sKP), aVD = smem_u32(sVD),
                  aWb = smem_u32(sWb), aGb = smem_u32(sGb), aA = smem_u32(sA), aT = smem_u32(sT);
@@ -138,6 +158,11 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   tc_fence_before();       \
   __syncthreads();
 
+  float lse_nx = 0.f, delta_nx = 0.f;
+  if ((p.nblk - 1) * kBlkB + row < p.N) {
+    lse_nx = p.lse[(int64_t)bh * p.N + (p.nblk - 1) * kBlkB + row];
+    delta_nx = p.delta[(int64_t)bh * p.N + (p.nblk - 1) * kBlkB + row];
+  }
   for (int I = p.nblk - 1; I >= K; --I) {
     const int i0 = I * kBlkB, irow = i0 + row;
     const bool diag = (I == K), first = (I == p.nblk - 1);
@@ -147,14 +172,17 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 #endif
     BPHASE_MARK(0);
 
-    const float lse_b = rvalid ? p.lse[(int64_t)bh * p.N + irow] * kLog2e : 0.f;
-    const float delta_i = rvalid ? p.delta[(int64_t)bh * p.N + irow] : 0.f;
-    mbar_wait(&bar_load, ph_load, abortp);
-    ph_load ^= 1;
-    BPHASE_MARK(1);
-
-    // ---- M1: Z = Qu[K] @ Ku[I]^T
+    // the row statistics were fetched one step ahead (their latency hides behind the step before)
+    const float lse_b = lse_nx * kLog2e, delta_i = delta_nx;
+    if (I > K) {
+      const int64_t nrow = (int64_t)bh * p.N + irow - kBlkB;   // rows of block I-1 always exist
+      lse_nx = p.lse[nrow];
+      delta_nx = p.delta[nrow];
+    }
+    // ---- M1: Z = Qu[K] @ Ku[I]^T   (Ku[I] was fetched during the last phase of the step before)
     if (tid == 0) {
+      mbar_wait(&bar_kn, ph_load, abortp);
+      BPHASE_MARK(1);
       tc_fence_after();
       gemm_kk_t<1>(tmem + C_S, aQu, aKP, ID_SQ_KK, false);
       mma_commit(&bar_mma);
@@ -178,19 +206,21 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 
     // ---- M2: peel W_K -= A @ Vu[I];  T = Qc[I] @ Vu[I]^T
     if (tid == 0) {
+      mbar_wait(&bar_load, ph_load, abortp);   // Qc[I], Vu[I]
+      BPHASE_MARK(21);
       tc_fence_after();
-      // The reduce of the step before must have finished reading its staging tiles before they are
-      // written again: slot 2 and Wb by the threads once this phase's products are done, Vc|dO by
-      // the loads issued here (they are needed at the fifth phase).
-      bulk_wait_read0();
-      mbar_expect_tx(&bar_vd, 2 * OPB);
-      tma_load_4d(sVc, &m_vc, &bar_vd, 0, k0, h, b);
-      tma_load_4d(sdO, &m_do, &bar_vd, 0, i0, h, b);
       gemm_km_t<8>(tmem + C_W, aA, aVu, ID_D_KM_NEG, true);
       gemm_kk_t<1>(tmem + C_S, aQc, aVu, ID_SQ_KK, false);
       mma_commit(&bar_mma);
     }
+    // The reduces of the step before must have finished reading their staging tiles before these are
+    // written again.  A reduce takes a few thousand cycles to drain, so each issuing lane waits for its
+    // own as late as the first overwrite allows: here for dqc and dku (Wb and slot 2 are written by the
+    // pass below), after the next products are issued for dvu (Vc|dO is re-loaded there).
+    if ((cc == 1 || cc == 2) && quarter == 0 && lane == 0) bulk_wait_read0();
     MMA_WAIT();
+    BPHASE_MARK(22);
+    __syncthreads();
     BPHASE_MARK(4);
     {  // masked T (rows i, columns j <= i), unscaled
       float v[32];
@@ -215,6 +245,10 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       if (!diag) gemm_kk_t<1>(tmem + C_S, aQc, aWb, ID_SQ_KK, false);
       gemm_kk_t<2>(tmem + C_S, aT, aA, ID_SQ_KK, !diag);
       mma_commit(&bar_mma);
+      bulk_wait_read0();   // this thread's dvu reduce of the step before has read Vc|dO's slot
+      mbar_expect_tx(&bar_vd, 2 * OPB);
+      tma_load_4d(sVc, &m_vc, &bar_vd, 0, k0, h, b);   // needed at the fifth phase
+      tma_load_4d(sdO, &m_do, &bar_vd, 0, i0, h, b);
     }
     MMA_WAIT();
     BPHASE_MARK(6);
@@ -347,42 +381,77 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     SMEM_TO_MMA_SYNC();
     BPHASE_MARK(15);
 
-    // ---- M9: X += dT @ Vu[I];  X2 = A^T @ Gb + dT^T @ Qc[I];  X3 = dZ^T @ Qu[K];  dqu += dZ @ Ku[I]
+    // ---- M9: dqu += dZ @ Ku[I];  X2 = dT^T @ Qc[I] + A^T @ Gb;  X += dT @ Vu[I];  X3 = dZ^T @ Qu[K]
+    // Three commits.  The first covers every product that reads a per-step input tile, so the next
+    // step's Qc, Vu, Ku are fetched right behind it, ahead of the reduces in the TMA queue (a reduce
+    // takes thousands of cycles to drain and loads issued behind one wait for it).  After each commit the
+    // query-block gradient it completes is staged as fp32 panels in an operand slot that is dead by then
+    // and handed to a TMA reduce (whole lines at L2 instead of scattered atomics): chunk group 1 takes
+    // dqc (into Wb + the spare half of slot 4), group 2 dku (into slot 2, which held dZ), group 0 - the
+    // issuing thread's, busy until the end - dvu (into Vc|dO, which held dT and is re-loaded last in the
+    // next step); group 3 fetches the next tiles and refreshes the 16-bit copy of G.
     if (tid == 0) {
       tc_fence_after();
+      gemm_mm_t<8>(tmem + C_X2, aVD, aQc, ID_D_MM, false);
       gemm_km_t<8>(tmem + C_X, aVD, aVu, ID_D_KM, true);
-      if (!first) gemm_mm_t<8>(tmem + C_X2, aA, aGb, ID_D_MM, false);
-      gemm_mm_t<8>(tmem + C_X2, aVD, aQc, ID_D_MM, !first);
-      gemm_mm_t<8>(tmem + C_X3, aT, aQu, ID_D_MM, false);
       mbar_wait(&bar_ku, ph_ku, abortp);
       gemm_km_t<8>(tmem + C_DQU, aT, aKP, ID_D_KM, !first);
+      mma_commit(&bar_x1);
+      gemm_mm_t<8>(tmem + C_X3, aT, aQu, ID_D_MM, false);
+      mma_commit(&bar_x2);
+      if (!first) gemm_mm_t<8>(tmem + C_X2, aA, aGb, ID_D_MM, true);
       mma_commit(&bar_mma);
     }
     ph_ku ^= 1;
-    MMA_WAIT();
-    BPHASE_MARK(16);
-    if (tid == 0 && I > K) {  // every per-step input tile is dead now: prefetch the next block's Qc, Vu, Ku
-      const int in0 = (I - 1) * kBlkB;
-      mbar_expect_tx(&bar_load, 3 * OPB);
-      tma_load_4d(sQc, &m_qc, &bar_load, 0, in0, h, b);
-      tma_load_4d(sVu, &m_vu, &bar_load, 0, in0, h, b);
-      tma_load_4d(sKP, &m_ku, &bar_load, 0, in0, h, b);
-    }
-    // dqc / dvu / dku of block I: staged as fp32 panels in operand slots that are dead now and are not
-    // written again before the second phase of the next step (slot 2, Vc|dO, Wb and the spare half of
-    // slot 4), then added to the workspace by TMA reduce - whole lines at L2 instead of scattered atomics
-    uint8_t* const stage0[3] = {sT, sVD, sWb};
-    uint8_t* const stage1[3] = {sT + kPanelB, sVD + kPanelB, sKP + kPanelB};
-    if (cc < 3) {
-      const uint32_t col = (cc == 0) ? C_X : (cc == 1 ? C_X2 : C_X3);
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        float v[32];
-        tmem_ld32(trow + col + c * 32, v);
-        tmem_ld_wait();
-        store_row32_f32(c == 0 ? stage0[cc] : stage1[cc], row, v);
+    const bool issuer = (quarter == 0 && lane == 0);   // threads 0, 128, 256 issue the reduces
+    if (cc == 1) {
+      mbar_wait(&bar_x1, ph_x, abortp);
+      tc_fence_after();
+      stage_f32_tile(trow + C_X, sWb, sKP + kPanelB, row);
+      fence_async_smem();
+      group_sync(1);
+      if (issuer) {
+        tma_reduce_add_3d(&m_acc_dqc, sWb, 0, i0, bh);
+        tma_reduce_add_3d(&m_acc_dqc, sKP + kPanelB, 32, i0, bh);
+        bulk_commit();
       }
-    } else {  // chunk group 3: 16-bit copy of G including block I, for the next (lower) block
+    } else if (cc == 2) {
+      mbar_wait(&bar_x2, ph_x, abortp);
+      tc_fence_after();
+      stage_f32_tile(trow + C_X3, sT, sT + kPanelB, row);
+      fence_async_smem();
+      group_sync(2);
+      if (issuer) {
+        tma_reduce_add_3d(&m_acc_dku, sT, 0, i0, bh);
+        tma_reduce_add_3d(&m_acc_dku, sT + kPanelB, 32, i0, bh);
+        bulk_commit();
+      }
+    } else if (cc == 3) {
+      mbar_wait(&bar_x1, ph_x, abortp);   // Qc[I], Vu[I], Ku[I] are consumed
+      if (tid == kPrefetchTid && I > K) {
+        const int in0 = i0 - kBlkB;
+        mbar_expect_tx(&bar_kn, OPB);
+        tma_load_4d(sKP, &m_ku, &bar_kn, 0, in0, h, b);
+        mbar_expect_tx(&bar_load, 2 * OPB);
+        tma_load_4d(sQc, &m_qc, &bar_load, 0, in0, h, b);
+        tma_load_4d(sVu, &m_vu, &bar_load, 0, in0, h, b);
+      }
+    }
+    ph_x ^= 1;
+    ph_load ^= 1;
+    BPHASE_MARK(16);
+    MMA_WAIT();
+    BPHASE_MARK(17);
+    if (cc == 0) {
+      stage_f32_tile(trow + C_X2, sVD, sVD + kPanelB, row);
+      fence_async_smem();
+      group_sync(3);
+      if (issuer) {
+        tma_reduce_add_3d(&m_acc_dvu, sVD, 0, i0, bh);
+        tma_reduce_add_3d(&m_acc_dvu, sVD + kPanelB, 32, i0, bh);
+        bulk_commit();
+      }
+    } else if (cc == 3) {  // 16-bit copy of G including block I, for the next (lower) block
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         float v[32];
@@ -391,19 +460,12 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
         store_row32<T>(sGb, kPanelB, row, c * 32, v);
       }
     }
+    BPHASE_MARK(18);
+    BPHASE_MARK(19);
     SMEM_TO_MMA_SYNC();
-    if (tid == 0) {
-      tma_reduce_add_3d(&m_acc_dqc, stage0[0], 0, i0, bh);
-      tma_reduce_add_3d(&m_acc_dqc, stage1[0], 32, i0, bh);
-      tma_reduce_add_3d(&m_acc_dvu, stage0[1], 0, i0, bh);
-      tma_reduce_add_3d(&m_acc_dvu, stage1[1], 32, i0, bh);
-      tma_reduce_add_3d(&m_acc_dku, stage0[2], 0, i0, bh);
-      tma_reduce_add_3d(&m_acc_dku, stage1[2], 32, i0, bh);
-      bulk_commit();
-    }
-    BPHASE_MARK(17);
+    BPHASE_MARK(20);
   }
-  if (tid == 0) bulk_wait0();
+  if (cc < 3 && quarter == 0 && lane == 0) bulk_wait0();
 #undef MMA_WAIT
 #undef SMEM_TO_MMA_SYNC
 

@@ -113,3 +113,63 @@ extern "C" int castle_selftest_mma(int32_t mode, const void* x, const void* y, f
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : cuda_fail(e, "castle_selftest_mma launch");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Issue-to-completion cost of one tensor-core instruction per operand form and width: `reps`
+// back-to-back products of shape 128 x n x 16 (operands are whatever the shared memory holds;
+// only the timing matters), one commit, cycles from first issue to completion.
+namespace castle {
+__global__ void __launch_bounds__(128) castle_mma_rate_kernel(int form, int n, int reps, long long* cycles, int32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  // eight panels: A in 0..1 (128 rows or 128 columns), B in 2..5 (up to 256 rows, or 256 columns = 4 panels)
+  for (int i = tid; i < 8 * (int)kPanel / 4; i += 128) reinterpret_cast<uint32_t*>(smem)[i] = 0x3c003c00u;  // finite values
+  if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); abort_flag = 0; }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 256); tmem_relinquish(); }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  if (tid == 0) {
+    const uint32_t xa = smem_u32(smem), ya = smem_u32(smem + 2 * kPanel);
+    const bool a_mn = form == 2 || form == 3, b_mn = form == 1 || form == 2;
+    const uint32_t idesc = make_idesc(128, n, 1, a_mn, b_mn, false);
+    const uint64_t dx = a_mn ? desc_mnmajor(xa, kPanel) : desc_kmajor(xa);
+    const uint64_t dy = b_mn ? desc_mnmajor(ya, kPanel) : desc_kmajor(ya);
+    const long long t0 = clock64();
+    for (int r = 0; r < reps; ++r) {
+      const int k = r & 3;  // walk the four 16-element steps of a panel like the kernels do
+      mma_ss(tmem, dx + (uint64_t)((a_mn ? 2048 * k : 32 * k) >> 4), dy + (uint64_t)((b_mn ? 2048 * k : 32 * k) >> 4), idesc, r > 0);
+    }
+    const long long t1 = clock64();
+    mma_commit(&bar);
+    mbar_wait(&bar, 0, &abort_flag);
+    const long long t2 = clock64();
+    cycles[0] = t1 - t0;  // issue only
+    cycles[1] = t2 - t0;  // issue to completion
+  }
+  __syncthreads();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+  if (tid == 0 && abort_flag) atomicOr(status, CASTLE_STATUS_WAIT_TIMEOUT);
+}
+}  // namespace castle
+
+extern "C" int castle_selftest_mma_rate(int32_t form, int32_t n, int32_t reps, long long* cycles, int32_t* status,
+                                        void* stream) {
+  if (form < 0 || form > 3 || (n != 64 && n != 128 && n != 192 && n != 256) || reps < 1 || reps > 4096)
+    return reject("castle_selftest_mma_rate: bad arguments");
+  if (!cycles || !status) return reject("castle_selftest_mma_rate: null pointer");
+  size_t smem = 8 * kPanel + 1024;
+  cudaError_t e = cudaFuncSetAttribute(castle_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return cuda_fail(e, "castle_selftest_mma_rate attribute");
+  castle_mma_rate_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(form, n, reps, cycles, status);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : cuda_fail(e, "castle_selftest_mma_rate launch");
+}

@@ -20,16 +20,19 @@ from . import _lib as L
 
 PHASES = ["wait for Qc/Vu/Ku", "MMA Z", "gate A", "MMA peel, T", "masked T, Wb", "MMA Su", "penalty, silu'",
           "MMA Sc", "P", "MMA dvc, dP", "dS, dSu", "MMA dA (+dkc, X)", "dZ", "MMA G, dT", "masked dT",
-          "MMA X, X2, X3, dqu", "stage + issue reduce"]
+          "issue X3, dqu, X2, X (3 commits)", "wait for the last commit", "stage dqc, issue its reduce", "-",
+          "end barrier"]
 
 
 def main():
+    extra = [a for a in sys.argv[1:] if a.startswith("-D")]   # e.g. -DCASTLE_TIMING_SKIP_REDUCE (wrong results, timing only)
+    sys.argv = [a for a in sys.argv if not a.startswith("-D")]
     B, H, N = (int(a) for a in sys.argv[1:4]) if len(sys.argv) >= 4 else (4, 16, 4096)
     d = 64
     out = Path(tempfile.mkdtemp()) / "libcastle_timing.so"
     srcs = [str(L.CSRC / f) for f in ("api.cu", "fwd.cu", "bwd.cu", "bwd128.cu")]
     subprocess.run([L._nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-shared", "-Xcompiler",
-                    "-fPIC", "-DCASTLE_PHASE_TIMING", "-o", str(out)] + srcs, check=True)
+                    "-fPIC", "-DCASTLE_PHASE_TIMING", "-o", str(out)] + extra + srcs, check=True)
     lib = ctypes.CDLL(str(out))
     for name in ("castle_fwd", "castle_bwd", "castle_fwd_workspace_bytes", "castle_bwd_workspace_bytes"):
         fn = getattr(lib, name)
@@ -61,8 +64,19 @@ def main():
         rc = lib.castle_bwd(ctypes.byref(prob), *[ctypes.byref(x) for x in a], lse.data_ptr(), wst.data_ptr(),
                             *[ctypes.byref(x) for x in gr], ws.data_ptr(), ws.numel(), st.data_ptr(), None)
         assert rc == 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        lib.castle_bwd(ctypes.byref(prob), *[ctypes.byref(x) for x in a], lse.data_ptr(), wst.data_ptr(),
+                       *[ctypes.byref(x) for x in gr], ws.data_ptr(), ws.numel(), st.data_ptr(), None)
+    e1.record()
     torch.cuda.synchronize()
-    t = ws[need:need + 8 * 32 * 8].view(torch.int64).cpu().view(8, 32)[1:7, :18]   # steps 1..6 of CTA (0,0)
+    print(f"castle_bwd (all four launches, timing build {' '.join(extra)}): {e0.elapsed_time(e1) / 5:.3f} ms per call")
+    raw = ws[need:need + 8 * 32 * 8].view(torch.int64).cpu().view(8, 32)[1:7]
+    print("  within 'MMA peel, T': wait for Qc/Vu %.0f, products %.0f, group barrier (reduce drain) %.0f" % (
+        (raw[:, 21] - raw[:, 3]).double().mean(), (raw[:, 22] - raw[:, 21]).double().mean(),
+        (raw[:, 4] - raw[:, 22]).double().mean()))
+    t = raw[:, :21]   # steps 1..6 of CTA (0,0)
     dt = (t[:, 1:] - t[:, :-1]).double().mean(0)
     print(f"castle_bwd_kernel<bf16,64>  B={B} H={H} N={N}: cycles per phase, CTA (0,0), mean of tile steps 1-6")
     for name, c in zip(PHASES, dt.tolist()):
