@@ -25,3 +25,30 @@ def test_selftest_mma(mode):
     ref = [xf @ yf.T, xf @ yf, xf.T @ yf, xf.T @ yf.T, 1.0 - xf @ yf.T][op]
     err = (d - ref).abs().max().item()
     assert err < 1e-3, f"mode {mode}: max err {err}"
+
+
+@pytest.mark.parametrize("form", range(4))
+@pytest.mark.parametrize("n", [64, 128, 256])
+def test_mma_rate_runs_and_is_sane(form, n):
+    """The rate micro-benchmark finishes with a clean status and a plausible cost per instruction
+    (a 128 x n x 16 product cannot beat n/2 cycles on this part, and 4x that would mean a broken loop)."""
+    from lookahead_keys_attention_b200 import _lib
+    from lookahead_keys_attention_b200.mma_rate import measure
+    lib = _lib.load()
+    cyc = torch.zeros(2, dtype=torch.int64, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _, t1 = measure(lib, form, n, 32, cyc, st)
+    _, t2 = measure(lib, form, n, 160, cyc, st)
+    per = (t2 - t1) / 128
+    assert 0.9 * n / 2 <= per <= 2 * n, per
+
+
+def test_mma_rate_rejects_bad_arguments():
+    from lookahead_keys_attention_b200 import _lib
+    lib = _lib.load()
+    cyc = torch.zeros(2, dtype=torch.int64, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.castle_selftest_mma_rate(4, 128, 8, cyc.data_ptr(), st.data_ptr(), None) < 0
+    assert lib.castle_selftest_mma_rate(0, 96, 8, cyc.data_ptr(), st.data_ptr(), None) < 0
+    assert lib.castle_selftest_mma_rate(0, 128, 0, cyc.data_ptr(), st.data_ptr(), None) < 0
+    assert lib.castle_selftest_mma_rate(0, 128, 8, None, st.data_ptr(), None) < 0
