@@ -366,16 +366,22 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 // tensor pipe or on a barrier.  To fit, only Qu[K] stays resident: Kc[K] and Vc[K] are re-fetched by
 // TMA each step into slots that have just died (Kc over the masked T once Su is done, Vc over Qc[I]
 // once Sc is done); both fetches hide behind the elementwise pass that follows their issue.
-// Warp w owns TMEM lanes 32*(w%4).. and the 64-column half w/4 of a 128-column accumulator.
-constexpr int kFwd2Threads = 256;
+// Warp w owns TMEM lanes 32*(w%4).. and the column group w/4 of a 128-column accumulator: with G = 2
+// groups (256 threads) a thread works on 64 values of every 128x128 tile, with G = 4 (512 threads, 64
+// registers each) on 32, which halves the dependent work per pass.
 constexpr uint32_t kFwd2Smem = 7 * kPanelBytes + 256;   // 112 KB of tiles + barriers
+#ifndef CASTLE_FWD_GROUPS
+#define CASTLE_FWD_GROUPS 2   // measured: 4 groups (512 threads, 63 registers) run the bench forward in 1.10 ms, 2 in 1.01 ms
+#endif
+constexpr int kFwd2Groups = CASTLE_FWD_GROUPS;
 
-template <typename T>
-__global__ void __launch_bounds__(kFwd2Threads, 2)
+template <typename T, int G>
+__global__ void __launch_bounds__(G * 128, 2)
 castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
                       const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
                       const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu) {
   constexpr int D = 64;
+  constexpr int NCH = 4 / G;   // 32-column chunks of a 128-column tile per thread
   constexpr uint32_t OPB = kPanelBytes;
   constexpr uint32_t TM_COLS = 256;
   constexpr uint32_t COL_W = 0, COL_S = 64, COL_O = 192;
@@ -398,10 +404,11 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
   // row max / row sum exchange between the two threads of a row: over the second half of the T slot,
   // dead from the end of the Su product until the next step's masked T is written
   float (*red_max)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sVuT + OPB);
-  float (*red_sum)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sVuT + OPB + 2 * kBlk * sizeof(float));
+  float (*red_sum)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sVuT + OPB + G * kBlk * sizeof(float));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int quarter = warp & 3, half = warp >> 2;
+  const int quarter = warp & 3, grp = warp >> 2;
+  const int cbase = grp * NCH * 32;
   const int row = quarter * 32 + lane;
   const int bh = blockIdx.x, K = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
@@ -456,6 +463,10 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
   for (int I = K; I < p.nblk; ++I) {
     const int i0 = I * kBlk;
     const bool diag = (I == K), last = (I == p.nblk - 1);
+#ifdef CASTLE_PHASE_TIMING
+    const int tstep = I - K;
+#endif
+    PHASE_MARK(0);
 
     // ---- Z[K,I] = Qu[K] @ Ku[I]^T
     if (tid == 0) {
@@ -465,9 +476,10 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       mma_commit(bar_mma);
     }
     F2_MMA_WAIT();
+    PHASE_MARK(1);
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {  // gate A = sigmoid(scale * Z), kept for j > k; over Ku[I]
-      const int c0 = half * 64 + c * 32;
+    for (int c = 0; c < NCH; ++c) {  // gate A = sigmoid(scale * Z), kept for j > k; over Ku[I]
+      const int c0 = cbase + c * 32;
       float v[32];
       tmem_ld32(trow + COL_S + c0, v);
       tmem_ld_wait();
@@ -480,6 +492,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       store_row32<T>(sKuA, kPanelBytes, row, c0, v);
     }
     F2_SYNC();
+    PHASE_MARK(2);
 
     // ---- W_K += A @ Vu[I]   and   T[I,I] = Qc[I] @ Vu[I]^T
     if (tid == 0) {
@@ -491,9 +504,10 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       mma_commit(bar_mma);
     }
     F2_MMA_WAIT();
+    PHASE_MARK(3);
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {  // masked T (j <= i), unscaled; over Vu[I]
-      const int c0 = half * 64 + c * 32;
+    for (int c = 0; c < NCH; ++c) {  // masked T (j <= i), unscaled; over Vu[I]
+      const int c0 = cbase + c * 32;
       float v[32];
       tmem_ld32(trow + COL_S + c0, v);
       tmem_ld_wait();
@@ -502,6 +516,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       store_row32<T>(sVuT, kPanelBytes, row, c0, v);
     }
     F2_SYNC();
+    PHASE_MARK(4);
 
     // ---- Su/scale = Qc[I] @ Wb^T + Tm @ A^T
     if (tid == 0) {
@@ -511,13 +526,14 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       mma_commit(bar_mma);
     }
     F2_MMA_WAIT();
+    PHASE_MARK(5);
     if (tid == 0) {  // the masked T is consumed: fetch Kc[K] over its first half
       mbar_expect_tx(bar_kc, OPB);
       tma_load_4d(sVuT, &m_kc, bar_kc, 0, k0, h, b);
     }
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {  // penalty -silu(Su)/scale back into the accumulator
-      const int c0 = half * 64 + c * 32;
+    for (int c = 0; c < NCH; ++c) {  // penalty -silu(Su)/scale back into the accumulator
+      const int c0 = cbase + c * 32;
       float v[32];
       tmem_ld32(trow + COL_S + c0, v);
       tmem_ld_wait();
@@ -525,14 +541,15 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       for (int j = 0; j < 32; ++j) v[j] = -v[j] * sigmoid_t<T>(v[j] * p.scale);
       tmem_st32(trow + COL_S + c0, v);
     }
-    {  // refresh the 16-bit copy of W (now including block I)
+    if (grp < 2) {  // refresh the 16-bit copy of W (now including block I)
       float v[32];
-      tmem_ld32(trow + COL_W + half * 32, v);
+      tmem_ld32(trow + COL_W + grp * 32, v);
       tmem_ld_wait();
-      store_row32<T>(sWb, kPanelBytes, row, half * 32, v);
+      store_row32<T>(sWb, kPanelBytes, row, grp * 32, v);
     }
     tmem_st_wait();
     F2_SYNC();
+    PHASE_MARK(6);
 
     // ---- S/scale = penalty + Qc[I] @ Kc[K]^T
     if (tid == 0) {
@@ -542,6 +559,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       mma_commit(bar_mma);
     }
     F2_MMA_WAIT();
+    PHASE_MARK(7);
     if (tid == 0) {  // Qc[I] and Kc[K] are consumed: fetch Vc[K] over Qc, and the next Vu over Kc
       mbar_expect_tx(bar_vc, OPB);
       tma_load_4d(sQV, &m_vc, bar_vc, 0, k0, h, b);
@@ -549,37 +567,41 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
     const int irow = i0 + row;
     float mrow, lsum = 0.f;
     {
-      float v0[32], v1[32];
-      const int c0 = half * 64;
-      tmem_ld32(trow + COL_S + c0, v0);
-      tmem_ld32(trow + COL_S + c0 + 32, v1);
+      float v[NCH][32];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) tmem_ld32(trow + COL_S + cbase + c * 32, v[c]);
       tmem_ld_wait();
       if (diag) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v0[j] = (c0 + j <= row) ? v0[j] : -INFINITY;
-          v1[j] = (c0 + 32 + j <= row) ? v1[j] : -INFINITY;
-        }
-      }
-      float mx = fmaxf(v0[0], v1[0]);
+        for (int c = 0; c < NCH; ++c)
 #pragma unroll
-      for (int j = 1; j < 32; ++j) mx = fmaxf(mx, fmaxf(v0[j], v1[j]));
-      red_max[half][row] = mx;
+          for (int j = 0; j < 32; ++j) v[c][j] = (cbase + c * 32 + j <= row) ? v[c][j] : -INFINITY;
+      }
+      float mx = v[0][0];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, v[c][j]);
+      red_max[grp][row] = mx;
       __syncthreads();
-      mx = fmaxf(red_max[0][row], red_max[1][row]);
+#pragma unroll
+      for (int g = 0; g < G; ++g) mx = fmaxf(mx, red_max[g][row]);
       mrow = mx * p.scale;
       const float mb = mx * sl2;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        v0[j] = ex2_approx(fmaf(v0[j], sl2, -mb));
-        v1[j] = ex2_approx(fmaf(v1[j], sl2, -mb));
-        lsum += v0[j] + v1[j];
+      for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          v[c][j] = ex2_approx(fmaf(v[c][j], sl2, -mb));
+          lsum += v[c][j];
+        }
       }
-      red_sum[half][row] = lsum;
-      store_row32<T>(sKuA, kPanelBytes, row, c0, v0);
-      store_row32<T>(sKuA, kPanelBytes, row, c0 + 32, v1);
+      red_sum[grp][row] = lsum;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) store_row32<T>(sKuA, kPanelBytes, row, cbase + c * 32, v[c]);
     }
     F2_SYNC();
+    PHASE_MARK(8);
 
     // ---- O_partial = P @ Vc[K]
     if (tid == 0) {
@@ -589,12 +611,16 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       mma_commit(bar_mma);
     }
     const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;
-    if (half == 0 && irow < p.N) {
+    if (grp == 0 && irow < p.N) {
       float2* ml = reinterpret_cast<float2*>(p.part_ml) + tile * kBlk + row;
-      *ml = make_float2(mrow, red_sum[0][row] + red_sum[1][row]);
+      float l = red_sum[0][row];
+#pragma unroll
+      for (int g = 1; g < G; ++g) l += red_sum[g][row];
+      *ml = make_float2(mrow, l);
     }
     fence_async_smem();  // the exchange buffer is read here and written by TMA (next Vu) below
     F2_MMA_WAIT();
+    PHASE_MARK(9);
     if (tid == 0 && !last) {  // every slot of this step is dead: fetch the next step's Qc, Ku, Vu
       const int in0 = i0 + kBlk;
       mbar_expect_tx(bar_qc, OPB);
@@ -604,10 +630,10 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       mbar_expect_tx(bar_vu, OPB);
       tma_load_4d(sVuT, &m_vu, bar_vu, 0, in0, h, b);
     }
-    {
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.part_o) + (tile * kBlk + row) * D + half * 32);
+    if (grp < 2) {
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.part_o) + (tile * kBlk + row) * D + grp * 32);
       float v[32];
-      tmem_ld32(trow + COL_O + half * 32, v);
+      tmem_ld32(trow + COL_O + grp * 32, v);
       tmem_ld_wait();
       if (irow < p.N) {
 #pragma unroll
@@ -619,14 +645,15 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
     ph_ld ^= 1;
     tc_fence_before();
     __syncthreads();
+    PHASE_MARK(10);
   }
 #undef F2_MMA_WAIT
 #undef F2_SYNC
 
   // ---- W_K is now U[K]
-  if (p.u_out.ptr != nullptr || p.w_state != nullptr) {
+  if (grp < 2 && (p.u_out.ptr != nullptr || p.w_state != nullptr)) {
     tc_fence_after();
-    const int c0 = half * 32;
+    const int c0 = grp * 32;
     float v[32];
     tmem_ld32(trow + COL_W + c0, v);
     tmem_ld_wait();
@@ -710,13 +737,14 @@ __global__ void __launch_bounds__(256) castle_fwd_merge_kernel(const FwdParams p
 
 template <typename T>
 static int launch_fwd_d64(const FwdParams& p, const CUtensorMap* maps, cudaStream_t st) {
+  constexpr int G = kFwd2Groups;
   {  // per device, so set on every call (cheap)
-    cudaError_t e = cudaFuncSetAttribute(castle_fwd_kernel_d64<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwd2Smem);
+    cudaError_t e = cudaFuncSetAttribute(castle_fwd_kernel_d64<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwd2Smem);
     if (e != cudaSuccess) return cuda_fail(e, "castle_fwd attribute");
   }
   dim3 grid(p.B * p.H, p.nblk);
   ev_start(CASTLE_KERNEL_FWD, st);
-  castle_fwd_kernel_d64<T><<<grid, kFwd2Threads, kFwd2Smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+  castle_fwd_kernel_d64<T, G><<<grid, G * 128, kFwd2Smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
   ev_stop(CASTLE_KERNEL_FWD, st);
   constexpr int ROWS = 256 / (64 / 8);
   dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);

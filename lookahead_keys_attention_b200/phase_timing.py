@@ -24,6 +24,10 @@ PHASES = ["wait for Qc/Vu/Ku", "MMA Z", "gate A", "MMA peel, T", "masked T, Wb",
           "end barrier"]
 
 
+FWD_PHASES = ["MMA Z", "gate A", "MMA W update, T", "masked T", "MMA Su", "penalty, Wb", "MMA Sc", "soft-max, P",
+              "MMA P.Vc", "partial store, end barrier"]
+
+
 def main():
     extra = [a for a in sys.argv[1:] if a.startswith("-D")]   # e.g. -DCASTLE_TIMING_SKIP_REDUCE (wrong results, timing only)
     sys.argv = [a for a in sys.argv if not a.startswith("-D")]
@@ -56,6 +60,13 @@ def main():
     rc = lib.castle_fwd(ctypes.byref(prob), *[ctypes.byref(x) for x in keep], lse.data_ptr(), None, 0, wst.data_ptr(),
                         wsf.data_ptr(), wsf.numel(), st.data_ptr(), None)
     assert rc == 0, lib.castle_last_error()
+    torch.cuda.synchronize()
+    tf = wsf[need_f:need_f + 8 * 16 * 8].view(torch.int64).cpu().view(8, 16)[1:7, :11]
+    df = (tf[:, 1:] - tf[:, :-1]).double().mean(0)
+    print(f"castle_fwd_kernel_d64<bf16>  B={B} H={H} N={N}: cycles per phase, CTA (0,0), mean of tile steps 1-6")
+    for name, c in zip(FWD_PHASES, df.tolist()):
+        print(f"  {name:24s} {c:8.0f}")
+    print(f"  {'total':24s} {df.sum().item():8.0f}")
     need = lib.castle_bwd_workspace_bytes(ctypes.byref(prob))
     ws = torch.zeros(need + 8192, dtype=torch.uint8, device=dev)
     a = [desc(t) for t in (qc, kc, vc, qu, ku, vu, o, do)]
