@@ -60,7 +60,14 @@ def main():
     rc = lib.castle_fwd(ctypes.byref(prob), *[ctypes.byref(x) for x in keep], lse.data_ptr(), None, 0, wst.data_ptr(),
                         wsf.data_ptr(), wsf.numel(), st.data_ptr(), None)
     assert rc == 0, lib.castle_last_error()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        lib.castle_fwd(ctypes.byref(prob), *[ctypes.byref(x) for x in keep], lse.data_ptr(), None, 0, wst.data_ptr(),
+                       wsf.data_ptr(), wsf.numel(), st.data_ptr(), None)
+    e1.record()
     torch.cuda.synchronize()
+    print(f"castle_fwd (both launches, timing build {' '.join(extra)}): {e0.elapsed_time(e1) / 5:.3f} ms per call")
     tf = wsf[need_f:need_f + 8 * 16 * 8].view(torch.int64).cpu().view(8, 16)[1:7, :11]
     df = (tf[:, 1:] - tf[:, :-1]).double().mean(0)
     print(f"castle_fwd_kernel_d64<bf16>  B={B} H={H} N={N}: cycles per phase, CTA (0,0), mean of tile steps 1-6")
