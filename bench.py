@@ -312,9 +312,9 @@ def run_ours(args):
                     "bwd_main_ms": round(bwd_ms, 4), "bwd_main_tflops": round(bwd_tflops, 2)},
         "roofline": {"kernel": "castle_bwd_kernel", "bound": "tensor", "achieved": round(bwd_tflops, 2),
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(bwd_tflops / peaks["tflops"], 4),
-                     # dram read+write bytes per launch: ncu capture of the B=2 case (1.068 GB), which grows
+                     # dram read+write bytes per launch: ncu capture of the B=2 case (1.052 GB), which grows
                      # in proportion to the (batch, head) pairs a launch processes
-                     "traffic": int(1.068e9 / 32 * bs * hs) if (N, d) == (4096, 64) else None,
+                     "traffic": int(1.052e9 / 32 * bs * hs) if (N, d) == (4096, 64) else None,
                      "peak_source": f"{peaks['source']} bf16 burst"},
         "clocks": clocks.summary(),
     }
