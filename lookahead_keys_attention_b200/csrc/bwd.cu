@@ -51,8 +51,6 @@ __device__ __forceinline__ void stage_f32_tile(uint32_t taddr, uint8_t* panel0, 
 #ifdef CASTLE_TIMING_SKIP_REDUCE
 #define tma_reduce_add_3d(...) do { } while (0)
 #endif
-// Barrier over the 128 threads (four warps) of one chunk group.
-__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)

@@ -22,6 +22,11 @@ constexpr int kB128Threads = 512;
 constexpr uint32_t kSlot = 2 * kPanelB;                      // 32 KB
 constexpr size_t kB128Smem = 7 * kSlot + 1024;
 
+// Timing experiments only (never in the shipped library): drop the reduces to see what they cost.
+#ifdef CASTLE_TIMING_SKIP_REDUCE
+#define tma_reduce_add_3d(...) do { } while (0)
+#endif
+
 #define B128_MMA_WAIT()                  \
   mbar_wait(&bar_mma, ph_mma, abortp);   \
   ph_mma ^= 1;                           \
@@ -72,6 +77,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
   const int bh = blockIdx.x, K = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
   const int k0 = K * kBlkB, krow = k0 + row;
+  const bool issuer = (quarter == 0 && lane == 0);   // threads 0, 128, 256, 384: one reduce each per step
 
   if (tid == 0) {
     mbar_init(&bar_a, 1); mbar_init(&bar_b, 1); mbar_init(&bar_vu2, 1); mbar_init(&bar_mma, 1);
@@ -142,18 +148,18 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       }
       store_row32<T>(s1, kPanelB, row, c0, v);
     }
+    if (issuer) bulk_wait_read0();  // this lane's dqc panel of the step before (in s5|s6) has been read
     B128_SYNC();
 
     // ---- M1: peel W -= A @ Vu[I];  T = Qc[I] @ Vu[I]^T
     if (tid == 0) {
       tc_fence_after();
-      bulk_wait_read0();  // the dqc staging of the step before (s5, s6) has been read
-      mbar_expect_tx(&bar_b, 2 * kSlot);
-      load_tile<2>(s5, &m_vc, &bar_b, k0, h, b);
-      load_tile<2>(s6, &m_do, &bar_b, i0, h, b);
       gemm_km_t<8>(tmem + C_W, a1, a2, ID_KM_NEG, true);
       gemm_kk_t<2>(tmem + C_S, a3, a2, ID_KK, false);
       mma_commit(&bar_mma);
+      mbar_expect_tx(&bar_b, 2 * kSlot);   // needed at the fifth phase; issued behind the products
+      load_tile<2>(s5, &m_vc, &bar_b, k0, h, b);
+      load_tile<2>(s6, &m_do, &bar_b, i0, h, b);
     }
     B128_MMA_WAIT();
     {  // masked T -> s2 (over Vu); 16-bit copy of the peeled state -> s0 (over Qu)
@@ -227,16 +233,16 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     if (tid == 0) {
       mbar_wait(&bar_b, ph_b, abortp);
       tc_fence_after();
+      mbar_expect_tx(&bar_vu2, kSlot);   // armed here, the two loads are issued below by other lanes
       gemm_mm_t<8>(tmem + C_DVC, a2, a6, ID_MM, !first);
       gemm_kk_t<2>(tmem + C_S, a6, a5, ID_KK, false);
       mma_commit(&bar_mma);
     }
     ph_b ^= 1;
     B128_MMA_WAIT();
-    if (tid == 0) {  // P is consumed: Vu[I] comes back into s2 for the last product
-      mbar_expect_tx(&bar_vu2, kSlot);
-      load_tile<2>(s2, &m_vu, &bar_vu2, i0, h, b);
-    }
+    // P is consumed: Vu[I] comes back into s2 for the last product (one panel per lane: a TMA
+    // instruction costs its issuing thread ~150 cycles)
+    if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s2 + (warp == 9) * kPanelB, &m_vu, &bar_vu2, (warp == 9) * 64, i0, h, b);
     {  // dS -> s5 (over Vc), dSu -> s6 (over dO)
       float v[32], w[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -276,6 +282,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     if (tid == 0) {
       mbar_wait(&bar_vu2, ph_vu2, abortp);
       tc_fence_after();
+      if (I > K) mbar_expect_tx(&bar_a, 4 * kSlot);   // armed here, the eight loads are issued below
       gemm_km_t<8>(tmem + C_S, a5, a4, ID_KM, false);
       if (!diag) gemm_km_t<8>(tmem + C_S, a6, a0, ID_KM, true);
       gemm_km_t<8>(tmem + C_S, a1, a2, ID_KM, true);
@@ -283,29 +290,29 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     ph_vu2 ^= 1;
     B128_MMA_WAIT();
-    if (tid == 0 && I > K) {  // s0..s4 are dead: prefetch the next block's tiles
-      const int in0 = (I - 1) * kBlkB;
-      mbar_expect_tx(&bar_a, 5 * kSlot);
-      load_tile<2>(s0, &m_qu, &bar_a, k0, h, b);
-      load_tile<2>(s1, &m_ku, &bar_a, in0, h, b);
-      load_tile<2>(s2, &m_vu, &bar_a, in0, h, b);
-      load_tile<2>(s3, &m_qc, &bar_a, in0, h, b);
-      load_tile<2>(s4, &m_kc, &bar_a, k0, h, b);
+    if (lane == 0 && warp < 8 && I > K) {  // s0..s3 are dead: prefetch the next block's Qu, Ku, Vu, Qc
+      const int in0 = (I - 1) * kBlkB;        // (Kc[K] stays in s4); one panel per lane of eight warps
+      const int t = warp >> 1, pn = warp & 1;
+      const CUtensorMap* m = t == 0 ? &m_qu : (t == 1 ? &m_ku : (t == 2 ? &m_vu : &m_qc));
+      tma_load_4d(smem + t * kSlot + pn * kPanelB, m, &bar_a, pn * 64, t == 0 ? k0 : in0, h, b);
     }
-    {  // stage dqc[I] as four fp32 panels over s5|s6 and add it to the workspace by TMA reduce
+    {  // stage dqc[I] as four fp32 panels over s5|s6 and add it to the workspace by TMA reduce:
+       // chunk group cc stages panel cc and one of its lanes issues that panel's reduce
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
       tmem_ld_wait();
       store_row32_f32(s5 + cc * kPanelB, row, v);
+      fence_async_smem();
+      group_sync(1 + cc);
+      if (issuer) {
+        tma_reduce_add_3d(&m_acc_dqc, s5 + cc * kPanelB, cc * 32, i0, bh);
+        bulk_commit();
+      }
     }
-    B128_SYNC();
-    if (tid == 0) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tma_reduce_add_3d(&m_acc_dqc, s5 + c * kPanelB, c * 32, i0, bh);
-      bulk_commit();
-    }
+    tc_fence_before();
+    __syncthreads();
   }
-  if (tid == 0) bulk_wait0();
+  if (issuer) bulk_wait0();
 
   // ---- dkc (x scale) and dvc of the key block
   {
@@ -373,6 +380,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
   const int bh = blockIdx.x, K = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
   const int k0 = K * kBlkB, krow = k0 + row;
+  const bool issuer = (quarter == 0 && lane == 0);   // threads 0, 128, 256, 384: chunk group cc's reduces
 
   if (tid == 0) {
     mbar_init(&bar_a, 1); mbar_init(&bar_kc, 1); mbar_init(&bar_ku2, 1); mbar_init(&bar_qu2, 1); mbar_init(&bar_mma, 1);
@@ -406,19 +414,22 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
                  a3 = smem_u32(s3), a4 = smem_u32(s4);
   const float sl2 = p.scale * kLog2e;
 
+  if (tid == 0) mbar_expect_tx(&bar_a, 6 * kSlot);
+  __syncthreads();
   for (int I = p.nblk - 1; I >= K; --I) {
     const int i0 = I * kBlkB, irow = i0 + row;
     const bool diag = (I == K), first = (I == p.nblk - 1);
     const bool rvalid = irow < p.N;
-    if (tid == 0) {
-      bulk_wait_read0();  // the staging tiles of the step before have been read by the reduces
-      mbar_expect_tx(&bar_a, 6 * kSlot);
-      load_tile<2>(s0, &m_qu, &bar_a, k0, h, b);
-      load_tile<2>(sA, &m_ku, &bar_a, i0, h, b);
-      load_tile<2>(s1, &m_vu, &bar_a, i0, h, b);
-      load_tile<2>(s2, &m_qc, &bar_a, i0, h, b);
-      load_tile<2>(s3, &m_do, &bar_a, i0, h, b);
-      load_tile<2>(s4, &m_vc, &bar_a, k0, h, b);
+    // The staging tiles of the step before must have been read by the reduces: each issuing lane
+    // waits for its own, then twelve lanes of twelve warps fetch one 16 KB panel each (a TMA
+    // instruction costs its issuing thread ~150 cycles; the barrier was armed in the step before).
+    if (issuer) bulk_wait_read0();
+    __syncthreads();
+    if (lane == 0 && warp < 12) {
+      const int t = warp >> 1, pn = warp & 1;
+      uint8_t* dst = (t == 0 ? s0 : t == 1 ? sA : t == 2 ? s1 : t == 3 ? s2 : t == 4 ? s3 : s4) + pn * kPanelB;
+      const CUtensorMap* m = t == 0 ? &m_qu : t == 1 ? &m_ku : t == 2 ? &m_vu : t == 3 ? &m_qc : t == 4 ? &m_do : &m_vc;
+      tma_load_4d(dst, m, &bar_a, pn * 64, (t == 0 || t == 5) ? k0 : i0, h, b);
     }
     const float lse_b = rvalid ? p.lse[(int64_t)bh * p.N + irow] * kLog2e : 0.f;
     const float delta_i = rvalid ? p.delta[(int64_t)bh * p.N + irow] : 0.f;
@@ -427,16 +438,15 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     if (tid == 0) {
       mbar_wait(&bar_a, ph_a, abortp);
       tc_fence_after();
+      mbar_expect_tx(&bar_kc, kSlot);   // armed here; the loads are issued below by two other lanes
       gemm_kk_t<2>(tmem + C_S, a0, aA, ID_KK, false);
       gemm_kk_t<2>(tmem + C_X, a3, a4, ID_KK, false);
       mma_commit(&bar_mma);
     }
     ph_a ^= 1;
     B128_MMA_WAIT();
-    if (tid == 0) {  // Qu is consumed: Kc[K] -> s0
-      mbar_expect_tx(&bar_kc, kSlot);
-      load_tile<2>(s0, &m_kc, &bar_kc, k0, h, b);
-    }
+    // Qu is consumed: Kc[K] -> s0
+    if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s0 + (warp == 9) * kPanelB, &m_kc, &bar_kc, (warp == 9) * 64, k0, h, b);
     float dpv[32];  // dP of this thread's 32 entries, kept until dS is formed
     {
       float v[32];
@@ -532,6 +542,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     // ---- M4: dA/scale = Gb @ Vu[I]^T + dSu^T @ Tm;  G += dSu^T @ Qc[I];  dT = dSu @ A
     if (tid == 0) {
       tc_fence_after();
+      mbar_expect_tx(&bar_ku2, kSlot);   // armed here; the loads are issued below by two other lanes
       if (!first) gemm_kk_t<2>(tmem + C_S, aG, a1, ID_KK, false);
       gemm_mm_t<8>(tmem + C_S, a4, a3, ID_MM, !first);
       gemm_mm_t<8>(tmem + C_G, a4, a2, ID_MM, !first);
@@ -539,10 +550,8 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       mma_commit(&bar_mma);
     }
     B128_MMA_WAIT();
-    if (tid == 0) {  // dSu is consumed: Ku[I] -> s4 for the dqu product
-      mbar_expect_tx(&bar_ku2, kSlot);
-      load_tile<2>(s4, &m_ku, &bar_ku2, i0, h, b);
-    }
+    // dSu is consumed: Ku[I] -> s4 for the dqu product
+    if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s4 + (warp == 9) * kPanelB, &m_ku, &bar_ku2, (warp == 9) * 64, i0, h, b);
     {  // dZ = dA A (1 - A) -> s3 (over the masked T); masked dT -> s0 (over Kc)
       float v[32], a[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -562,6 +571,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     // ---- M5: dvu[I] (unscaled) = A^T @ Gb + dT^T @ Qc[I];  dqu[K] part = dZ @ Ku[I]
     if (tid == 0) {
       tc_fence_after();
+      mbar_expect_tx(&bar_qu2, kSlot);   // armed here; the loads are issued below by two other lanes
       if (!first) gemm_mm_t<8>(tmem + C_X, aA, aG, ID_MM, false);
       gemm_mm_t<8>(tmem + C_X, a0, a2, ID_MM, !first);
       mbar_wait(&bar_ku2, ph_ku2, abortp);
@@ -570,10 +580,8 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     ph_ku2 ^= 1;
     B128_MMA_WAIT();
-    if (tid == 0) {  // the gate is consumed: Qu[K] -> sA for the dku product
-      mbar_expect_tx(&bar_qu2, kSlot);
-      load_tile<2>(sA, &m_qu, &bar_qu2, k0, h, b);
-    }
+    // the gate is consumed: Qu[K] -> sA for the dku product
+    if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(sA + (warp == 9) * kPanelB, &m_qu, &bar_qu2, (warp == 9) * 64, k0, h, b);
     {  // stage dvu[I] over s1|s2 and the dqu part over s0|s4 (two fp32 panels each)
       float v[32];
       tmem_ld32(trow + C_X + c0, v);
@@ -583,15 +591,15 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       tmem_ld_wait();
       store_row32_f32((cc < 2 ? s0 : s4) + (cc & 1) * kPanelB, row, v);
     }
-    B128_SYNC();
-    if (tid == 0) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tma_reduce_add_3d(&m_acc_dvu, (c < 2 ? s1 : s2) + (c & 1) * kPanelB, c * 32, i0, bh);
-        tma_reduce_add_3d(&m_acc_dqu, (c < 2 ? s0 : s4) + (c & 1) * kPanelB, c * 32, k0, bh);
-      }
+    fence_async_smem();
+    group_sync(1 + cc);
+    if (issuer) {  // chunk group cc staged panel cc of both tiles; its lane issues their reduces
+      tma_reduce_add_3d(&m_acc_dvu, (cc < 2 ? s1 : s2) + (cc & 1) * kPanelB, cc * 32, i0, bh);
+      tma_reduce_add_3d(&m_acc_dqu, (cc < 2 ? s0 : s4) + (cc & 1) * kPanelB, cc * 32, k0, bh);
       bulk_commit();
     }
+    tc_fence_before();
+    __syncthreads();
 
     // ---- M6: dku[I] (unscaled) = dZ^T @ Qu[K]
     if (tid == 0) {
@@ -599,11 +607,12 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       tc_fence_after();
       gemm_mm_t<8>(tmem + C_X, a3, aA, ID_MM, false);
       mma_commit(&bar_mma);
-      bulk_wait_read0();  // dvu staging (s1|s2) is free again
+      if (I > K) mbar_expect_tx(&bar_a, 6 * kSlot);   // the next step's six tiles
     }
     ph_qu2 ^= 1;
+    if (issuer) bulk_wait_read0();  // this lane's dvu panel (in s1|s2) has been read: the slot is free again
     B128_MMA_WAIT();
-    __syncthreads();  // orders thread 0's wait on the reduce before everybody's staging stores
+    __syncthreads();  // orders the issuing lanes' waits before everybody's staging stores
     {
       float v[32];
       tmem_ld32(trow + C_X + c0, v);
@@ -614,14 +623,16 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       tmem_ld_wait();
       store_row32<T>(sG, kPanelB, row, c0, v);
     }
-    B128_SYNC();
-    if (tid == 0) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tma_reduce_add_3d(&m_acc_dku, (c < 2 ? s1 : s2) + (c & 1) * kPanelB, c * 32, i0, bh);
+    fence_async_smem();
+    group_sync(1 + cc);
+    if (issuer) {
+      tma_reduce_add_3d(&m_acc_dku, (cc < 2 ? s1 : s2) + (cc & 1) * kPanelB, cc * 32, i0, bh);
       bulk_commit();
     }
+    tc_fence_before();
+    __syncthreads();
   }
-  if (tid == 0) bulk_wait0();
+  if (issuer) bulk_wait0();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);

@@ -78,13 +78,13 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   uint8_t* sVc = sKc + OPB;
   uint8_t* sQc = sVc + OPB;
   uint8_t* sWb = sQc + OPB;
-  uint8_t* sKuA = sWb + OPB;   // Ku[I], then the gate A[K,I], then the soft-max numerators P
-  uint8_t* sVuT = sKuA + SQB;  // Vu[I], then the masked T[I,I]
+  uint8_t* sKuA = sWb + OPB;   // Ku[I], then the gate A[K,I]; Ku[I+1] arrives once Su is done
+  uint8_t* sVuT = sKuA + SQB;  // Vu[I], then the masked T[I,I], then the soft-max numerators P
   // row max / row sum exchange between the four threads of a row: 4 KB over Qc[I], which is dead
   // once the last product reading it (Sc) has completed and until the next step's TMA load
   float (*red_max)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sQc);
   float (*red_sum)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sQc + 4 * kBlk * sizeof(float));
-  __shared__ uint64_t bar_res, bar_load, bar_mma;
+  __shared__ uint64_t bar_res, bar_ku, bar_vu, bar_qc, bar_mma;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -98,7 +98,9 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 
   if (tid == 0) {
     mbar_init(&bar_res, 1);
-    mbar_init(&bar_load, 1);
+    mbar_init(&bar_ku, 1);
+    mbar_init(&bar_vu, 1);
+    mbar_init(&bar_qc, 1);
     mbar_init(&bar_mma, 1);
     mbar_fence_init();
     abort_flag = 0;
@@ -120,6 +122,17 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       tma_load_4d(sKc + pn * kPanelBytes, &m_kc, &bar_res, pn * 64, k0, h, b);
       tma_load_4d(sVc + pn * kPanelBytes, &m_vc, &bar_res, pn * 64, k0, h, b);
     }
+    // the first block's tiles; later blocks are fetched inside the step before, each as soon as its
+    // slot dies (a tile takes 2-4 thousand cycles from issue to arrival)
+    mbar_expect_tx(&bar_ku, OPB);
+    mbar_expect_tx(&bar_vu, OPB);
+    mbar_expect_tx(&bar_qc, OPB);
+#pragma unroll
+    for (int pn = 0; pn < NP; ++pn) {
+      tma_load_4d(sKuA + pn * kPanelBytes, &m_ku, &bar_ku, pn * 64, k0, h, b);
+      tma_load_4d(sVuT + pn * kPanelBytes, &m_vu, &bar_vu, pn * 64, k0, h, b);
+      tma_load_4d(sQc + pn * kPanelBytes, &m_qc, &bar_qc, pn * 64, k0, h, b);
+    }
   }
   mbar_wait(&bar_res, 0, abortp);
 
@@ -136,22 +149,18 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     const int tstep = I - K;
 #endif
     PHASE_MARK(0);
-    // ---- stream in Qc[I], Ku[I], Vu[I]
-    if (tid == 0) {
-      mbar_expect_tx(&bar_load, 3 * OPB);
-#pragma unroll
-      for (int pn = 0; pn < NP; ++pn) {
-        tma_load_4d(sQc + pn * kPanelBytes, &m_qc, &bar_load, pn * 64, i0, h, b);
-        tma_load_4d(sKuA + pn * kPanelBytes, &m_ku, &bar_load, pn * 64, i0, h, b);
-        tma_load_4d(sVuT + pn * kPanelBytes, &m_vu, &bar_load, pn * 64, i0, h, b);
-      }
-    }
-    mbar_wait(&bar_load, ph_load, abortp);
-    ph_load ^= 1;
-    PHASE_MARK(1);
+    const bool more = I + 1 < p.nblk;
+    const int in0 = i0 + kBlk;
+    // Qc[I] goes into its slot only now: that slot doubled as the soft-max exchange buffer until the end
+    // of the step before.  It is needed at the second product phase.  One panel per lane of two warps
+    // (a TMA instruction costs its issuing thread ~150 cycles); the barrier was armed in the step before.
+    if (I > K && lane == 0 && warp >= 4 && warp < 4 + NP)
+      tma_load_4d(sQc + (warp - 4) * kPanelBytes, &m_qc, &bar_qc, (warp - 4) * 64, i0, h, b);
 
     // ---- Z[K,I] = Qu[K] @ Ku[I]^T  (rows = keys k, columns = positions j)
     if (tid == 0) {
+      mbar_wait(&bar_ku, ph_load, abortp);
+      PHASE_MARK(1);
       tc_fence_after();
       gemm_kk_t<NP>(tmem + COL_S, aQu, aKuA, ID_SQ, false);
       mma_commit(&bar_mma);
@@ -179,6 +188,8 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 
     // ---- W_K += A @ Vu[I]   and   T[I,I] = Qc[I] @ Vu[I]^T
     if (tid == 0) {
+      mbar_wait(&bar_vu, ph_load, abortp);
+      mbar_wait(&bar_qc, ph_load, abortp);
       tc_fence_after();
       gemm_km_t<8>(tmem + COL_W, aKuA, aVuT, ID_D, !diag);
       gemm_kk_t<NP>(tmem + COL_S, aQc, aVuT, ID_SQ, false);
@@ -204,6 +215,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     // ---- Su/scale = Qc[I] @ Wb^T + Tm @ A^T   (Wb = 16-bit copy of W before this step's update)
     if (tid == 0) {
       tc_fence_after();
+      if (more) mbar_expect_tx(&bar_ku, OPB);   // armed here; the loads are issued below by other lanes
       if (!diag) gemm_kk_t<NP>(tmem + COL_S, aQc, aWb, ID_SQ, false);
       gemm_kk_t<2>(tmem + COL_S, aVuT, aKuA, ID_SQ, !diag);
       mma_commit(&bar_mma);
@@ -212,6 +224,9 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     ph_mma ^= 1;
     tc_fence_after();
     PHASE_MARK(6);
+    // the gate and the masked T are consumed: Ku[I+1] -> the gate's slot (P will go over the masked T)
+    if (more && lane == 0 && warp >= 4 && warp < 4 + NP)
+      tma_load_4d(sKuA + (warp - 4) * kPanelBytes, &m_ku, &bar_ku, (warp - 4) * 64, in0, h, b);
     {  // penalty -silu(Su)/scale goes back into the accumulator; Sc is then accumulated on top of it
       float v[32];
       tmem_ld32(trow + COL_S + c0, v);
@@ -272,7 +287,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
         v[j] = pe;
       }
       red_sum[cc][row] = lsum;
-      store_row32<T>(sKuA, kPanelBytes, row, c0, v);
+      store_row32<T>(sVuT, kPanelBytes, row, c0, v);
     }
     fence_async_smem();
     tc_fence_before();
@@ -282,7 +297,8 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     // ---- O_partial = P @ Vc[K]
     if (tid == 0) {
       tc_fence_after();
-      gemm_km_t<8>(tmem + COL_O, aKuA, aVc, ID_D, false);
+      if (more) { mbar_expect_tx(&bar_vu, OPB); mbar_expect_tx(&bar_qc, OPB); }   // loads issued by other lanes
+      gemm_km_t<8>(tmem + COL_O, aVuT, aVc, ID_D, false);
       mma_commit(&bar_mma);
     }
     const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;
@@ -295,6 +311,9 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     ph_mma ^= 1;
     tc_fence_after();
     PHASE_MARK(10);
+    // P is consumed: Vu[I+1] -> its slot
+    if (more && lane == 0 && warp >= 8 && warp < 8 + NP)
+      tma_load_4d(sVuT + (warp - 8) * kPanelBytes, &m_vu, &bar_vu, (warp - 8) * 64, in0, h, b);
     if (c0 < D) {
       uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.part_o) + (tile * kBlk + row) * D + c0);
       float v[32];
@@ -310,6 +329,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     fence_async_smem();  // the exchange buffer over Qc[I] was read by threads; TMA writes it next
     tc_fence_before();
     __syncthreads();
+    ph_load ^= 1;
     PHASE_MARK(11);
   }
 

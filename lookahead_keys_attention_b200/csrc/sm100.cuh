@@ -55,6 +55,9 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   *abort_flag = 1;
 }
 
+// Barrier over the 128 threads (four warps) of one chunk group; ids 1..15 (0 is __syncthreads).
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_async_smem() {  // generic-proxy smem writes -> async proxy (MMA/TMA) reads
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
