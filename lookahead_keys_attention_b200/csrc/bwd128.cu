@@ -27,6 +27,14 @@ constexpr size_t kB128Smem = 7 * kSlot + 1024;
 #define tma_reduce_add_3d(...) do { } while (0)
 #endif
 
+// Optional phase timing (debug builds only): thread 0 of CTA (0,0) stores clock64() at phase boundaries of
+// its first steps behind the fp32 workspace (key/value kernel at slot 0, lookahead kernel at slot 256).
+#ifdef CASTLE_PHASE_TIMING
+#define B128_MARK(base, i) do { if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && p.nblk - 1 - I < 8) p.timing[(base) + (p.nblk - 1 - I) * 32 + (i)] = clock64(); } while (0)
+#else
+#define B128_MARK(base, i) do { } while (0)
+#endif
+
 #define B128_MMA_WAIT()                  \
   mbar_wait(&bar_mma, ph_mma, abortp);   \
   ph_mma ^= 1;                           \
@@ -67,7 +75,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
   uint8_t* s4 = s3 + kSlot;        // Kc[K]
   uint8_t* s5 = s4 + kSlot;        // Vc[K] -> dS -> dqc staging
   uint8_t* s6 = s5 + kSlot;        // dO[I] -> dSu -> dqc staging
-  __shared__ uint64_t bar_a, bar_b, bar_vu2, bar_mma;
+  __shared__ uint64_t bar_a, bar_b, bar_vu2, bar_mma, bar_x1, bar_x2;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -81,6 +89,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
 
   if (tid == 0) {
     mbar_init(&bar_a, 1); mbar_init(&bar_b, 1); mbar_init(&bar_vu2, 1); mbar_init(&bar_mma, 1);
+    mbar_init(&bar_x1, 1); mbar_init(&bar_x2, 1);
     mbar_fence_init();
     abort_flag = 0;
   }
@@ -115,7 +124,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
   tc_fence_before();
   __syncthreads();
 
-  uint32_t ph_a = 0, ph_b = 0, ph_vu2 = 0, ph_mma = 0;
+  uint32_t ph_a = 0, ph_b = 0, ph_vu2 = 0, ph_mma = 0, ph_x = 0;
   const uint32_t a0 = smem_u32(s0), a1 = smem_u32(s1), a2 = smem_u32(s2), a3 = smem_u32(s3), a4 = smem_u32(s4),
                  a5 = smem_u32(s5), a6 = smem_u32(s6);
   const float sl2 = p.scale * kLog2e;
@@ -278,24 +287,32 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     B128_SYNC();
 
-    // ---- M6: dqc[I] (unscaled) = dS @ Kc[K] + dSu @ Wb + dT @ Vu[I]
+    // ---- M6: dqc[I] (unscaled) = dT @ Vu[I] + dSu @ Wb + dS @ Kc[K]
+    // Three commits, in the order in which the products free the per-step slots, so that the next
+    // block's tiles are fetched as early as possible (a tile takes 2-4 thousand cycles to arrive): behind
+    // the first Ku, Vu and Qc (s1, s2; s3's last reader, the dkc product issued in the phase before, is
+    // covered too), behind the second Qu (s0).  One 16 KB panel per lane of eight warps.
     if (tid == 0) {
       mbar_wait(&bar_vu2, ph_vu2, abortp);
       tc_fence_after();
-      if (I > K) mbar_expect_tx(&bar_a, 4 * kSlot);   // armed here, the eight loads are issued below
-      gemm_km_t<8>(tmem + C_S, a5, a4, ID_KM, false);
+      if (I > K) mbar_expect_tx(&bar_a, 4 * kSlot);   // armed here, the eight loads are issued by other lanes
+      gemm_km_t<8>(tmem + C_S, a1, a2, ID_KM, false);
+      mma_commit(&bar_x1);
       if (!diag) gemm_km_t<8>(tmem + C_S, a6, a0, ID_KM, true);
-      gemm_km_t<8>(tmem + C_S, a1, a2, ID_KM, true);
+      mma_commit(&bar_x2);
+      gemm_km_t<8>(tmem + C_S, a5, a4, ID_KM, true);
       mma_commit(&bar_mma);
     }
     ph_vu2 ^= 1;
-    B128_MMA_WAIT();
-    if (lane == 0 && warp < 8 && I > K) {  // s0..s3 are dead: prefetch the next block's Qu, Ku, Vu, Qc
-      const int in0 = (I - 1) * kBlkB;        // (Kc[K] stays in s4); one panel per lane of eight warps
-      const int t = warp >> 1, pn = warp & 1;
+    if (lane == 0 && warp < 8 && I > K) {
+      const int in0 = (I - 1) * kBlkB;
+      const int t = warp >> 1, pn = warp & 1;   // tile 0: Qu -> s0, 1: Ku -> s1, 2: Vu -> s2, 3: Qc -> s3
       const CUtensorMap* m = t == 0 ? &m_qu : (t == 1 ? &m_ku : (t == 2 ? &m_vu : &m_qc));
+      mbar_wait(t == 0 ? &bar_x2 : &bar_x1, ph_x, abortp);
       tma_load_4d(smem + t * kSlot + pn * kPanelB, m, &bar_a, pn * 64, t == 0 ? k0 : in0, h, b);
     }
+    ph_x ^= 1;
+    B128_MMA_WAIT();
     {  // stage dqc[I] as four fp32 panels over s5|s6 and add it to the workspace by TMA reduce:
        // chunk group cc stages panel cc and one of its lanes issues that panel's reduce
       float v[32];
@@ -423,8 +440,10 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     // The staging tiles of the step before must have been read by the reduces: each issuing lane
     // waits for its own, then twelve lanes of twelve warps fetch one 16 KB panel each (a TMA
     // instruction costs its issuing thread ~150 cycles; the barrier was armed in the step before).
+    B128_MARK(256, 0);
     if (issuer) bulk_wait_read0();
     __syncthreads();
+    B128_MARK(256, 1);
     if (lane == 0 && warp < 12) {
       const int t = warp >> 1, pn = warp & 1;
       uint8_t* dst = (t == 0 ? s0 : t == 1 ? sA : t == 2 ? s1 : t == 3 ? s2 : t == 4 ? s3 : s4) + pn * kPanelB;
@@ -437,6 +456,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     // ---- M0: Z = Qu[K] @ Ku[I]^T;  dP = dO[I] @ Vc[K]^T
     if (tid == 0) {
       mbar_wait(&bar_a, ph_a, abortp);
+      B128_MARK(256, 2);
       tc_fence_after();
       mbar_expect_tx(&bar_kc, kSlot);   // armed here; the loads are issued below by two other lanes
       gemm_kk_t<2>(tmem + C_S, a0, aA, ID_KK, false);
@@ -445,6 +465,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     ph_a ^= 1;
     B128_MMA_WAIT();
+    B128_MARK(256, 3);
     // Qu is consumed: Kc[K] -> s0
     if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s0 + (warp == 9) * kPanelB, &m_kc, &bar_kc, (warp == 9) * 64, k0, h, b);
     float dpv[32];  // dP of this thread's 32 entries, kept until dS is formed
@@ -462,6 +483,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       store_row32<T>(sA, kPanelB, row, c0, v);  // gate A (over Ku)
     }
     B128_SYNC();
+    B128_MARK(256, 4);
 
     // ---- M1: peel W -= A @ Vu[I];  T = Qc[I] @ Vu[I]^T
     if (tid == 0) {
@@ -471,6 +493,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       mma_commit(&bar_mma);
     }
     B128_MMA_WAIT();
+    B128_MARK(256, 5);
     {  // masked T -> s3 (over dO); 16-bit copy of the peeled state -> s4 (over Vc)
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -483,6 +506,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       store_row32<T>(s4, kPanelB, row, c0, v);
     }
     B128_SYNC();
+    B128_MARK(256, 6);
 
     // ---- M2: Su/scale = Qc[I] @ Wb^T + Tm @ A^T
     if (tid == 0) {
@@ -492,6 +516,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       mma_commit(&bar_mma);
     }
     B128_MMA_WAIT();
+    B128_MARK(256, 7);
     uint32_t dpk[16];
     {
       float v[32];
@@ -510,6 +535,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     tc_fence_before();
     __syncthreads();
+    B128_MARK(256, 8);
 
     // ---- M3: S/scale = penalty + Qc[I] @ Kc[K]^T
     if (tid == 0) {
@@ -520,6 +546,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     ph_kc ^= 1;
     B128_MMA_WAIT();
+    B128_MARK(256, 9);
     {  // P, dS = P (dP - delta), dSu = -dS silu'(Su) -> s4 (over Wb)
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -538,6 +565,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       store_row32<T>(s4, kPanelB, row, c0, v);
     }
     B128_SYNC();
+    B128_MARK(256, 10);
 
     // ---- M4: dA/scale = Gb @ Vu[I]^T + dSu^T @ Tm;  G += dSu^T @ Qc[I];  dT = dSu @ A
     if (tid == 0) {
@@ -550,6 +578,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       mma_commit(&bar_mma);
     }
     B128_MMA_WAIT();
+    B128_MARK(256, 11);
     // dSu is consumed: Ku[I] -> s4 for the dqu product
     if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s4 + (warp == 9) * kPanelB, &m_ku, &bar_ku2, (warp == 9) * 64, i0, h, b);
     {  // dZ = dA A (1 - A) -> s3 (over the masked T); masked dT -> s0 (over Kc)
@@ -567,6 +596,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       store_row32<T>(s0, kPanelB, row, c0, v);
     }
     B128_SYNC();
+    B128_MARK(256, 12);
 
     // ---- M5: dvu[I] (unscaled) = A^T @ Gb + dT^T @ Qc[I];  dqu[K] part = dZ @ Ku[I]
     if (tid == 0) {
@@ -580,6 +610,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     ph_ku2 ^= 1;
     B128_MMA_WAIT();
+    B128_MARK(256, 13);
     // the gate is consumed: Qu[K] -> sA for the dku product
     if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(sA + (warp == 9) * kPanelB, &m_qu, &bar_qu2, (warp == 9) * 64, k0, h, b);
     {  // stage dvu[I] over s1|s2 and the dqu part over s0|s4 (two fp32 panels each)
@@ -600,6 +631,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     tc_fence_before();
     __syncthreads();
+    B128_MARK(256, 14);
 
     // ---- M6: dku[I] (unscaled) = dZ^T @ Qu[K]
     if (tid == 0) {
@@ -613,6 +645,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     if (issuer) bulk_wait_read0();  // this lane's dvu panel (in s1|s2) has been read: the slot is free again
     B128_MMA_WAIT();
     __syncthreads();  // orders the issuing lanes' waits before everybody's staging stores
+    B128_MARK(256, 15);
     {
       float v[32];
       tmem_ld32(trow + C_X + c0, v);
@@ -631,6 +664,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     tc_fence_before();
     __syncthreads();
+    B128_MARK(256, 16);
   }
   if (issuer) bulk_wait0();
   tc_fence_before();

@@ -1,10 +1,10 @@
-"""Developer aid: per-phase cycle counts of the d=64 backward kernel.
+"""Developer aid: per-phase cycle counts of the parallel kernels.
 
 Builds a DEBUG copy of the library with -DCASTLE_PHASE_TIMING (thread 0 of CTA (0,0) stores
 clock64() at every phase boundary of its first eight tile steps behind the workspace), runs one
 forward and a few backward passes on random inputs and prints the cycles each phase took.
 
-    python -m lookahead_keys_attention_b200.phase_timing [B H N]
+    python -m lookahead_keys_attention_b200.phase_timing [B H N [d]] [-DMACRO ...]
 
 The shipped library is built without the flag; this never touches it.
 """
@@ -24,6 +24,11 @@ PHASES = ["wait for Qc/Vu/Ku", "MMA Z", "gate A", "MMA peel, T", "masked T, Wb",
           "end barrier"]
 
 
+LA_PHASES = ["wait: reduces of the step before drained", "issue loads, wait for the six tiles",
+             "MMA Z, dP", "gate A", "MMA peel, T", "masked T, Wb", "MMA Su", "penalty", "MMA Sc (+ wait Kc)",
+             "P, dS, dSu", "MMA dA, G, dT", "dZ, masked dT", "MMA dvu, dqu part (+ wait Ku)",
+             "stage dvu, dqu; issue reduces", "MMA dku (+ wait Qu, dvu reduce drained)", "stage dku, Gb; issue reduce"]
+
 FWD_PHASES = ["MMA Z", "gate A", "MMA W update, T", "masked T", "MMA Su", "penalty, Wb", "MMA Sc", "soft-max, P",
               "MMA P.Vc", "partial store, end barrier"]
 
@@ -32,7 +37,7 @@ def main():
     extra = [a for a in sys.argv[1:] if a.startswith("-D")]   # e.g. -DCASTLE_TIMING_SKIP_REDUCE (wrong results, timing only)
     sys.argv = [a for a in sys.argv if not a.startswith("-D")]
     B, H, N = (int(a) for a in sys.argv[1:4]) if len(sys.argv) >= 4 else (4, 16, 4096)
-    d = 64
+    d = int(sys.argv[4]) if len(sys.argv) >= 5 else 64
     out = Path(tempfile.mkdtemp()) / "libcastle_timing.so"
     srcs = [str(L.CSRC / f) for f in ("api.cu", "fwd.cu", "bwd.cu", "bwd128.cu")]
     subprocess.run([L._nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-shared", "-Xcompiler",
@@ -68,12 +73,13 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     print(f"castle_fwd (both launches, timing build {' '.join(extra)}): {e0.elapsed_time(e1) / 5:.3f} ms per call")
-    tf = wsf[need_f:need_f + 8 * 16 * 8].view(torch.int64).cpu().view(8, 16)[1:7, :11]
-    df = (tf[:, 1:] - tf[:, :-1]).double().mean(0)
-    print(f"castle_fwd_kernel_d64<bf16>  B={B} H={H} N={N}: cycles per phase, CTA (0,0), mean of tile steps 1-6")
-    for name, c in zip(FWD_PHASES, df.tolist()):
-        print(f"  {name:24s} {c:8.0f}")
-    print(f"  {'total':24s} {df.sum().item():8.0f}")
+    if d == 64:
+        tf = wsf[need_f:need_f + 8 * 16 * 8].view(torch.int64).cpu().view(8, 16)[1:7, :11]
+        df = (tf[:, 1:] - tf[:, :-1]).double().mean(0)
+        print(f"castle_fwd_kernel_d64<bf16>  B={B} H={H} N={N}: cycles per phase, CTA (0,0), mean of tile steps 1-6")
+        for name, c in zip(FWD_PHASES, df.tolist()):
+            print(f"  {name:24s} {c:8.0f}")
+        print(f"  {'total':24s} {df.sum().item():8.0f}")
     need = lib.castle_bwd_workspace_bytes(ctypes.byref(prob))
     ws = torch.zeros(need + 8192, dtype=torch.uint8, device=dev)
     a = [desc(t) for t in (qc, kc, vc, qu, ku, vu, o, do)]
@@ -90,6 +96,14 @@ def main():
     e1.record()
     torch.cuda.synchronize()
     print(f"castle_bwd (all four launches, timing build {' '.join(extra)}): {e0.elapsed_time(e1) / 5:.3f} ms per call")
+    if d == 128:
+        raw = ws[need + 2048:need + 2048 + 8 * 32 * 8].view(torch.int64).cpu().view(8, 32)[1:7, :17]
+        dt = (raw[:, 1:] - raw[:, :-1]).double().mean(0)
+        print(f"castle_bwd128_la_kernel<bf16>  B={B} H={H} N={N}: cycles per phase, CTA (0,0), mean of tile steps 1-6")
+        for name, c in zip(LA_PHASES, dt.tolist()):
+            print(f"  {name:44s} {c:8.0f}")
+        print(f"  {'total':44s} {dt.sum().item():8.0f}")
+        return
     raw = ws[need:need + 8 * 32 * 8].view(torch.int64).cpu().view(8, 32)[1:7]
     print("  within 'MMA peel, T': wait for Qc/Vu %.0f, products %.0f, group barrier (reduce drain) %.0f" % (
         (raw[:, 21] - raw[:, 3]).double().mean(), (raw[:, 22] - raw[:, 21]).double().mean(),
