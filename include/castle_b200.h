@@ -155,7 +155,8 @@ int castle_set_kernel_events(int32_t which, void* start_event, void* stop_event)
  * buffers; `d`: fp32 [128][128].  mode 0: d = x @ y^T; 1: d = x @ y;
  * 2: d = x^T @ y; 3: d = x^T @ y^T; 4: d = 1 - x @ y^T (preset accumulator,
  * negated operand); 5..8: as 0..3 with operands staged by TMA instead of
- * thread stores.
+ * thread stores; 9: d = x @ y^T and 10: d = x @ y with x read from tensor
+ * memory (packed 16-bit pairs) instead of shared memory.
  */
 int castle_selftest_mma(int32_t mode, const void* x, const void* y, float* d, int32_t* status, void* stream);
 

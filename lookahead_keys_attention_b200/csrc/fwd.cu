@@ -386,6 +386,12 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 // tensor pipe or on a barrier.  To fit, only Qu[K] stays resident: Kc[K] and Vc[K] are re-fetched by
 // TMA each step into slots that have just died (Kc over the masked T once Su is done, Vc over Qc[I]
 // once Sc is done); both fetches hide behind the elementwise pass that follows their issue.
+// The three products whose first operand is a tile the threads have just computed (gate A for the state
+// update, the masked T for the Su correction, P for P @ Vc) read it from TENSOR MEMORY, where the
+// threads put it as packed 16-bit pairs with tcgen05.st: that halves the shared-memory traffic of those
+// products (the port, not the tensor pipe, bounds a product with both operands in shared memory) and
+// saves the shared-memory copies of the masked T and of P.  The 64 packed columns alias accumulators
+// that are dead at that moment: gate and masked T over O, P over the first half of S.
 // Warp w owns TMEM lanes 32*(w%4).. and the column group w/4 of a 128-column accumulator: with G = 2
 // groups (256 threads) a thread works on 64 values of every 128x128 tile, with G = 4 (512 threads, 64
 // registers each) on 32, which halves the dependent work per pass.
@@ -509,8 +515,10 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = (c0 + j > row) ? v[j] : 0.f;
       }
-      store_row32<T>(sKuA, kPanelBytes, row, c0, v);
+      store_row32<T>(sKuA, kPanelBytes, row, c0, v);          // operand of the Su correction (read along rows)
+      tmem_st_packed32<T>(trow + COL_O + c0 / 2, v);          // first operand of the state update
     }
+    tmem_st_wait();
     F2_SYNC();
     PHASE_MARK(2);
 
@@ -519,7 +527,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       mbar_wait(bar_vu, ph_ld, abortp);
       mbar_wait(bar_qc, ph_ld, abortp);
       tc_fence_after();
-      gemm_km_t<8>(tmem + COL_W, aKuA, aVuT, ID_D, !diag);
+      gemm_tm_t<8>(tmem + COL_W, tmem + COL_O, aVuT, ID_D, !diag);
       gemm_kk_t<1>(tmem + COL_S, aQV, aVuT, ID_SQ, false);
       mma_commit(bar_mma);
     }
@@ -533,21 +541,23 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
-      store_row32<T>(sVuT, kPanelBytes, row, c0, v);
+      tmem_st_packed32<T>(trow + COL_O + c0 / 2, v);   // over the gate's packed copy, which the update has consumed
     }
-    F2_SYNC();
+    tmem_st_wait();
+    tc_fence_before();
+    __syncthreads();
     PHASE_MARK(4);
 
     // ---- Su/scale = Qc[I] @ Wb^T + Tm @ A^T
     if (tid == 0) {
       tc_fence_after();
       if (!diag) gemm_kk_t<1>(tmem + COL_S, aQV, aWb, ID_SQ, false);
-      gemm_kk_t<2>(tmem + COL_S, aVuT, aKuA, ID_SQ, !diag);
+      gemm_tk_t<2>(tmem + COL_S, tmem + COL_O, aKuA, ID_SQ, !diag);
       mma_commit(bar_mma);
     }
     F2_MMA_WAIT();
     PHASE_MARK(5);
-    if (tid == 0) {  // the masked T is consumed: fetch Kc[K] over its first half
+    if (tid == 0) {  // Vu[I] is long consumed: fetch Kc[K] into its slot
       mbar_expect_tx(bar_kc, OPB);
       tma_load_4d(sVuT, &m_kc, bar_kc, 0, k0, h, b);
     }
@@ -617,17 +627,21 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
         }
       }
       red_sum[grp][row] = lsum;
+      // P as packed pairs over the first 64 columns of S: every thread of the row has its values in
+      // registers since the barrier above, so the accumulator may be overwritten
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) store_row32<T>(sKuA, kPanelBytes, row, cbase + c * 32, v[c]);
+      for (int c = 0; c < NCH; ++c) tmem_st_packed32<T>(trow + COL_S + (cbase + c * 32) / 2, v[c]);
     }
-    F2_SYNC();
+    tmem_st_wait();
+    tc_fence_before();
+    __syncthreads();
     PHASE_MARK(8);
 
     // ---- O_partial = P @ Vc[K]
     if (tid == 0) {
       mbar_wait(bar_vc, ph_ld, abortp);
       tc_fence_after();
-      gemm_km_t<8>(tmem + COL_O, aKuA, aQV, ID_D, false);
+      gemm_tm_t<8>(tmem + COL_O, tmem + COL_S, aQV, ID_D, false);
       mma_commit(bar_mma);
     }
     const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;

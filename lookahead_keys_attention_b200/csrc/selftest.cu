@@ -1,7 +1,8 @@
 // Self test of the tensor-core building blocks: one 128x128x128 product through
 // every operand form the CASTLE kernels use (rows-contracted and
 // columns-contracted shared-memory operands, staged by thread stores or by TMA,
-// a preset accumulator and a negated operand).
+// a preset accumulator and a negated operand), plus the two forms whose first operand sits in tensor
+// memory as packed 16-bit pairs.
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -21,7 +22,8 @@ __global__ void __launch_bounds__(128) castle_selftest_kernel(int mode, const __
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const bool use_tma = mode >= 5;
+  const bool a_in_tmem = mode >= 9;   // 9: X (tensor memory) @ Y^T, 10: X (tensor memory) @ Y
+  const bool use_tma = mode >= 5 && !a_in_tmem;
   const int op = use_tma ? mode - 5 : mode;
 
   if (tid == 0) {
@@ -30,7 +32,7 @@ __global__ void __launch_bounds__(128) castle_selftest_kernel(int mode, const __
     mbar_fence_init();
     abort_flag = 0;
   }
-  if (warp == 0) { tmem_alloc(&tmem_base_s, 128); tmem_relinquish(); }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 256); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -54,6 +56,20 @@ __global__ void __launch_bounds__(128) castle_selftest_kernel(int mode, const __
     }
     fence_async_smem();
   }
+  if (a_in_tmem) {  // this thread's row of X as packed pairs into columns 128..191 of its lane
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      float pk[32];
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        uint4 q = *reinterpret_cast<const uint4*>(x + tid * 128 + c * 64 + j * 2);
+        pk[j] = __uint_as_float(q.x); pk[j + 1] = __uint_as_float(q.y);
+        pk[j + 2] = __uint_as_float(q.z); pk[j + 3] = __uint_as_float(q.w);
+      }
+      tmem_st32(tmem + ((uint32_t)(warp * 32) << 16) + 128 + c * 32, pk);
+    }
+    tmem_st_wait();
+  }
   if (op == 4) {  // preset the accumulator to 1.0
     float ones[32];
 #pragma unroll
@@ -72,6 +88,8 @@ __global__ void __launch_bounds__(128) castle_selftest_kernel(int mode, const __
       case 1: gemm_km(tmem, xa, kPanel, ya, kPanel, 8, make_idesc(128, 128, 1, false, true, false), false); break;
       case 2: gemm_mm(tmem, xa, kPanel, ya, kPanel, 8, make_idesc(128, 128, 1, true, true, false), false); break;
       case 3: gemm_mk(tmem, xa, kPanel, ya, kPanel, 8, make_idesc(128, 128, 1, true, false, false), false); break;
+      case 9: gemm_tk_t<2>(tmem, tmem + 128, ya, make_idesc(128, 128, 1, false, false, false), false); break;
+      case 10: gemm_tm_t<8>(tmem, tmem + 128, ya, make_idesc(128, 128, 1, false, true, false), false); break;
       default: gemm_kk(tmem, xa, kPanel, ya, kPanel, 2, make_idesc(128, 128, 1, false, false, true), true); break;
     }
     mma_commit(&bar_mma);
@@ -87,7 +105,7 @@ __global__ void __launch_bounds__(128) castle_selftest_kernel(int mode, const __
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 128);
+  if (warp == 0) tmem_dealloc(tmem, 256);
   if (tid == 0 && abort_flag) atomicOr(status, CASTLE_STATUS_WAIT_TIMEOUT);
 }
 
@@ -97,7 +115,7 @@ using namespace castle;
 
 extern "C" int castle_selftest_mma(int32_t mode, const void* x, const void* y, float* d, int32_t* status,
                                    void* stream) {
-  if (mode < 0 || mode > 8) return reject("castle_selftest_mma: mode %d out of range", mode);
+  if (mode < 0 || mode > 10) return reject("castle_selftest_mma: mode %d out of range", mode);
   if (!x || !y || !d || !status) return reject("castle_selftest_mma: null pointer");
   CUtensorMap mx, my;
   castle_tensor_t tx = {(void*)x, 128 * 128, 128 * 128, 128}, ty = {(void*)y, 128 * 128, 128 * 128, 128};

@@ -161,6 +161,17 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"((uint32_t)accum)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows x 16 elements) sits in tensor memory, row m in
+// lane m, elements 2j and 2j+1 packed in the low and high half of 32-bit column j (what a thread that owns
+// row m writes with tcgen05.st of packed pairs).  Halves the shared-memory traffic of the product.
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"((uint32_t)accum)
+      : "memory");
+}
 // Make an mbarrier complete once every MMA this thread issued so far has finished.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -224,6 +235,21 @@ template <> struct Elem<__half> {
   static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
   static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
 };
+
+// 32 values of a row as 16 packed 16-bit pairs into 16 consecutive columns of the thread's lane: the
+// layout a tensor-memory A operand wants (see mma_ts).
+template <typename T>
+__device__ __forceinline__ void tmem_st_packed32(uint32_t taddr, const float* v) {
+  uint32_t r[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) r[j] = Elem<T>::pack2(v[2 * j], v[2 * j + 1]);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
+      : "memory");
+}
 
 // ---------------------------------------------------------------- fast transcendentals
 __device__ __forceinline__ float tanh_approx(float x) {
@@ -309,6 +335,27 @@ __device__ __forceinline__ void gemm_km_t(uint32_t d_tmem, uint32_t x_addr, uint
     const uint64_t xo = (uint64_t)(((k >> 2) * (128 * 128) + 32 * (k & 3)) >> 4);
     mma_ss(d_tmem, dx + xo, dy + (uint64_t)((2048 * k) >> 4), idesc, accum || k > 0);
   }
+}
+// C[128 x N] (+)= X * Y^T with X in tensor memory (packed 16-bit pairs, 8 columns per 16-element step) and
+// Y [N rows][64*NPANELS] in shared memory read along its rows.
+template <int NPANELS>
+__device__ __forceinline__ void gemm_tk_t(uint32_t d_tmem, uint32_t x_tmem, uint32_t y_addr, uint32_t idesc, bool accum) {
+  const uint64_t dy = desc_kmajor(y_addr);
+#pragma unroll
+  for (int p = 0; p < NPANELS; ++p) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint64_t off = (uint64_t)((p * (128 * 128) + 32 * k) >> 4);
+      mma_ts(d_tmem, x_tmem + (p * 4 + k) * 8, dy + off, idesc, accum || p > 0 || k > 0);
+    }
+  }
+}
+// C[128 x N] (+)= X * Y with X in tensor memory and Y [Kc rows][N] in shared memory read down its columns.
+template <int KSTEPS>
+__device__ __forceinline__ void gemm_tm_t(uint32_t d_tmem, uint32_t x_tmem, uint32_t y_addr, uint32_t idesc, bool accum) {
+  const uint64_t dy = desc_mnmajor(y_addr, 128 * 128);
+#pragma unroll
+  for (int k = 0; k < KSTEPS; ++k) mma_ts(d_tmem, x_tmem + k * 8, dy + (uint64_t)((2048 * k) >> 4), idesc, accum || k > 0);
 }
 // C[128 x N] (+)= X^T * Y with X [Kc rows][128] and Y [Kc rows][N], both read down their columns.
 template <int KSTEPS>

@@ -7,7 +7,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("mode", range(9))
+@pytest.mark.parametrize("mode", range(11))
 def test_selftest_mma(mode):
     from lookahead_keys_attention_b200 import _lib
     lib = _lib.load()
@@ -21,8 +21,11 @@ def test_selftest_mma(mode):
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     xf, yf = x.float(), y.float()
-    op = mode - 5 if mode >= 5 else mode
-    ref = [xf @ yf.T, xf @ yf, xf.T @ yf, xf.T @ yf.T, 1.0 - xf @ yf.T][op]
+    if mode >= 9:   # first operand read from tensor memory
+        ref = xf @ yf.T if mode == 9 else xf @ yf
+    else:
+        op = mode - 5 if mode >= 5 else mode
+        ref = [xf @ yf.T, xf @ yf, xf.T @ yf, xf.T @ yf.T, 1.0 - xf @ yf.T][op]
     err = (d - ref).abs().max().item()
     assert err < 1e-3, f"mode {mode}: max err {err}"
 
