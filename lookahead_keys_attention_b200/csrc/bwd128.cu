@@ -387,7 +387,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
   uint8_t* s2 = s1 + kSlot;        // Qc[I] -> dvu / dku staging
   uint8_t* s3 = s2 + kSlot;        // dO[I] -> masked T -> dZ
   uint8_t* s4 = s3 + kSlot;        // Vc[K] -> Wb -> dSu -> Ku[I] -> dqu staging
-  __shared__ uint64_t bar_a, bar_kc, bar_ku2, bar_qu2, bar_mma;
+  __shared__ uint64_t bar_a, bar_v, bar_kc, bar_ku2, bar_qu2, bar_mma;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -397,10 +397,12 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
   const int bh = blockIdx.x, K = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
   const int k0 = K * kBlkB, krow = k0 + row;
-  const bool issuer = (quarter == 0 && lane == 0);   // threads 0, 128, 256, 384: chunk group cc's reduces
+  // one lane per chunk group issues that group's reduces and, once they have read their staging panels,
+  // refills the panels it owns; not thread 0, which must not be held up on its way to the next products
+  const bool issuer = (quarter == 1 && lane == 0);   // threads 32, 160, 288, 416
 
   if (tid == 0) {
-    mbar_init(&bar_a, 1); mbar_init(&bar_kc, 1); mbar_init(&bar_ku2, 1); mbar_init(&bar_qu2, 1); mbar_init(&bar_mma, 1);
+    mbar_init(&bar_a, 1); mbar_init(&bar_v, 1); mbar_init(&bar_kc, 1); mbar_init(&bar_ku2, 1); mbar_init(&bar_qu2, 1); mbar_init(&bar_mma, 1);
     mbar_fence_init();
     abort_flag = 0;
   }
@@ -426,30 +428,36 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
   tc_fence_before();
   __syncthreads();
 
-  uint32_t ph_a = 0, ph_kc = 0, ph_ku2 = 0, ph_qu2 = 0, ph_mma = 0;
+  uint32_t ph_a = 0, ph_kc = 0, ph_ku2 = 0, ph_qu2 = 0, ph_mma = 0;   // ph_a also serves bar_v
   const uint32_t aG = smem_u32(sG), aA = smem_u32(sA), a0 = smem_u32(s0), a1 = smem_u32(s1), a2 = smem_u32(s2),
                  a3 = smem_u32(s3), a4 = smem_u32(s4);
   const float sl2 = p.scale * kLog2e;
 
-  if (tid == 0) mbar_expect_tx(&bar_a, 6 * kSlot);
-  __syncthreads();
+  if (tid == 0) {  // the first block's tiles; later ones are fetched inside the step before (see the last phase)
+    const int il = (p.nblk - 1) * kBlkB;
+    mbar_expect_tx(&bar_a, 4 * kSlot);
+    load_tile<2>(s0, &m_qu, &bar_a, k0, h, b);
+    load_tile<2>(sA, &m_ku, &bar_a, il, h, b);
+    load_tile<2>(s3, &m_do, &bar_a, il, h, b);
+    load_tile<2>(s4, &m_vc, &bar_a, k0, h, b);
+    mbar_expect_tx(&bar_v, 2 * kSlot);
+    load_tile<2>(s1, &m_vu, &bar_v, il, h, b);
+    load_tile<2>(s2, &m_qc, &bar_v, il, h, b);
+  }
   for (int I = p.nblk - 1; I >= K; --I) {
     const int i0 = I * kBlkB, irow = i0 + row;
     const bool diag = (I == K), first = (I == p.nblk - 1);
     const bool rvalid = irow < p.N;
-    // The staging tiles of the step before must have been read by the reduces: each issuing lane
-    // waits for its own, then twelve lanes of twelve warps fetch one 16 KB panel each (a TMA
-    // instruction costs its issuing thread ~150 cycles; the barrier was armed in the step before).
+    // Vu[I] and Qc[I] go into the panels that held the dku staging of the step before: each issuing lane
+    // waits until its reduce has read its panel and refills exactly that panel (nobody else touches it),
+    // so no barrier is needed and the products below start without waiting for the drain.  The four
+    // tiles of the first phase were fetched during the step before.
     B128_MARK(256, 0);
-    if (issuer) bulk_wait_read0();
-    __syncthreads();
-    B128_MARK(256, 1);
-    if (lane == 0 && warp < 12) {
-      const int t = warp >> 1, pn = warp & 1;
-      uint8_t* dst = (t == 0 ? s0 : t == 1 ? sA : t == 2 ? s1 : t == 3 ? s2 : t == 4 ? s3 : s4) + pn * kPanelB;
-      const CUtensorMap* m = t == 0 ? &m_qu : t == 1 ? &m_ku : t == 2 ? &m_vu : t == 3 ? &m_qc : t == 4 ? &m_do : &m_vc;
-      tma_load_4d(dst, m, &bar_a, pn * 64, (t == 0 || t == 5) ? k0 : i0, h, b);
+    if (issuer && I < p.nblk - 1) {
+      bulk_wait_read0();
+      tma_load_4d((cc < 2 ? s1 : s2) + (cc & 1) * kPanelB, cc < 2 ? &m_vu : &m_qc, &bar_v, (cc & 1) * 64, i0, h, b);
     }
+    B128_MARK(256, 1);
     const float lse_b = rvalid ? p.lse[(int64_t)bh * p.N + irow] * kLog2e : 0.f;
     const float delta_i = rvalid ? p.delta[(int64_t)bh * p.N + irow] : 0.f;
 
@@ -487,6 +495,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
 
     // ---- M1: peel W -= A @ Vu[I];  T = Qc[I] @ Vu[I]^T
     if (tid == 0) {
+      mbar_wait(&bar_v, ph_a ^ 1, abortp);   // Vu[I], Qc[I] (ph_a was flipped after the first phase)
       tc_fence_after();
       gemm_km_t<8>(tmem + C_W, aA, a1, ID_KM_NEG, true);
       gemm_kk_t<2>(tmem + C_S, a2, a1, ID_KK, false);
@@ -639,13 +648,25 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       tc_fence_after();
       gemm_mm_t<8>(tmem + C_X, a3, aA, ID_MM, false);
       mma_commit(&bar_mma);
-      if (I > K) mbar_expect_tx(&bar_a, 6 * kSlot);   // the next step's six tiles
+      if (I > K) {  // the next step's tiles: four fetched below, two at the top of the next step
+        mbar_expect_tx(&bar_a, 4 * kSlot);
+        mbar_expect_tx(&bar_v, 2 * kSlot);
+      }
     }
     ph_qu2 ^= 1;
     if (issuer) bulk_wait_read0();  // this lane's dvu panel (in s1|s2) has been read: the slot is free again
     B128_MMA_WAIT();
     __syncthreads();  // orders the issuing lanes' waits before everybody's staging stores
     B128_MARK(256, 15);
+    // The reduces of dvu and of the dqu part have drained and the last product is done, so the slots of
+    // the next step's first phase are all free: Qu[K] -> s0, Ku[I-1] -> sA, dO[I-1] -> s3, Vc[K] -> s4, one
+    // 16 KB panel per lane of eight warps; they arrive while dku is staged.
+    if (lane == 0 && warp < 8 && I > K) {
+      const int t = warp >> 1, pn = warp & 1, in0 = i0 - kBlkB;
+      uint8_t* dst = (t == 0 ? s0 : t == 1 ? sA : t == 2 ? s3 : s4) + pn * kPanelB;
+      const CUtensorMap* m = t == 0 ? &m_qu : t == 1 ? &m_ku : t == 2 ? &m_do : &m_vc;
+      tma_load_4d(dst, m, &bar_a, pn * 64, (t == 0 || t == 3) ? k0 : in0, h, b);
+    }
     {
       float v[32];
       tmem_ld32(trow + C_X + c0, v);

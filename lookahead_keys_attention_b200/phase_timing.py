@@ -24,7 +24,7 @@ PHASES = ["wait for Qc/Vu/Ku", "MMA Z", "gate A", "MMA peel, T", "masked T, Wb",
           "end barrier"]
 
 
-LA_PHASES = ["wait: reduces of the step before drained", "issue loads, wait for the six tiles",
+LA_PHASES = ["(issuing lanes refill the dku staging panels with Vu, Qc)", "wait for Qu, Ku, dO, Vc (fetched in the step before)",
              "MMA Z, dP", "gate A", "MMA peel, T", "masked T, Wb", "MMA Su", "penalty", "MMA Sc (+ wait Kc)",
              "P, dS, dSu", "MMA dA, G, dT", "dZ, masked dT", "MMA dvu, dqu part (+ wait Ku)",
              "stage dvu, dqu; issue reduces", "MMA dku (+ wait Qu, dvu reduce drained)", "stage dku, Gb; issue reduce"]
