@@ -384,8 +384,8 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 // CTAs share an SM.  Each CTA's step is a serial chain of products and elementwise passes; with two
 // resident chains one CTA's transcendental work fills the time the other spends waiting on the
 // tensor pipe or on a barrier.  To fit, only Qu[K] stays resident: Kc[K] and Vc[K] are re-fetched by
-// TMA each step into slots that have just died (Kc over the masked T once Su is done, Vc over Qc[I]
-// once Sc is done); both fetches hide behind the elementwise pass that follows their issue.
+// TMA each step into slots that have just died (Kc over Vu[I] once Su is done, Vc over Qc[I] once Sc
+// is done); both fetches hide behind the elementwise pass that follows their issue.
 // The three products whose first operand is a tile the threads have just computed (gate A for the state
 // update, the masked T for the Su correction, P for P @ Vc) read it from TENSOR MEMORY, where the
 // threads put it as packed 16-bit pairs with tcgen05.st: that halves the shared-memory traffic of those
@@ -394,7 +394,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 // that are dead at that moment: gate and masked T over O, P over the first half of S.
 // Warp w owns TMEM lanes 32*(w%4).. and the column group w/4 of a 128-column accumulator: with G = 2
 // groups (256 threads) a thread works on 64 values of every 128x128 tile, with G = 4 (512 threads, 64
-// registers each) on 32, which halves the dependent work per pass.
+// registers each) on 32 (measured slower, see below).
 constexpr uint32_t kFwd2Smem = 7 * kPanelBytes + 256;   // 112 KB of tiles + barriers
 #ifndef CASTLE_FWD_GROUPS
 #define CASTLE_FWD_GROUPS 2   // measured: 4 groups (512 threads, 63 registers) run the bench forward in 1.10 ms, 2 in 1.01 ms
@@ -420,8 +420,8 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
   uint8_t* sQu = smem;                 // resident
   uint8_t* sQV = sQu + OPB;            // Qc[I], then Vc[K]
   uint8_t* sWb = sQV + OPB;
-  uint8_t* sKuA = sWb + OPB;           // Ku[I] -> gate A -> P   (32 KB)
-  uint8_t* sVuT = sKuA + 2 * OPB;      // Vu[I] -> masked T (32 KB) -> Kc[K] in the first half
+  uint8_t* sKuA = sWb + OPB;           // Ku[I] -> gate A (32 KB; P lives in tensor memory)
+  uint8_t* sVuT = sKuA + 2 * OPB;      // Vu[I] -> Kc[K] in the first half (the masked T lives in tensor memory)
   uint64_t* bars = reinterpret_cast<uint64_t*>(sVuT + 2 * OPB);
   uint64_t *bar_qu = bars, *bar_qc = bars + 1, *bar_ku = bars + 2, *bar_vu = bars + 3, *bar_kc = bars + 4,
            *bar_vc = bars + 5, *bar_mma = bars + 6;
