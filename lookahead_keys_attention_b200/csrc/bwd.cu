@@ -358,15 +358,17 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     // ---- M8: G += dSu^T @ Qc[I];  dT = dSu @ A
     if (tid == 0) {
       tc_fence_after();
-      gemm_mm_t<8>(tmem + C_G, aKP, aQc, ID_D_MM, !first);
+      // dT first and committed alone: masking it overlaps the G update, which the next phase's first
+      // commit covers (dSu stays in slot 4 until then)
       gemm_km_t<8>(tmem + C_S, aKP, aA, ID_SQ_KM, false);
-      mma_commit(&bar_mma);   // covers the G update too: dSu's slot is re-loaded with Ku right after
+      mma_commit(&bar_mma);
+      gemm_mm_t<8>(tmem + C_G, aKP, aQc, ID_D_MM, !first);
     }
     MMA_WAIT();
     BPHASE_MARK(14);
-    if (tid == 0) {  // dSu is consumed: bring Ku[I] back into the first half of slot 4 for the dqu product
+    if (tid == 0) {  // Ku[I] comes back for the dqu product, into Wb's slot (its last reader is covered by the commit above)
       mbar_expect_tx(&bar_ku, OPB);
-      tma_load_4d(sKP, &m_ku, &bar_ku, 0, i0, h, b);
+      tma_load_4d(sWb, &m_ku, &bar_ku, 0, i0, h, b);
     }
     {  // masked dT (rows i, columns j <= i) -> slot 3 (over dS)
       float v[32];
@@ -393,7 +395,7 @@ castle_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       gemm_mm_t<8>(tmem + C_X2, aVD, aQc, ID_D_MM, false);
       gemm_km_t<8>(tmem + C_X, aVD, aVu, ID_D_KM, true);
       mbar_wait(&bar_ku, ph_ku, abortp);
-      gemm_km_t<8>(tmem + C_DQU, aT, aKP, ID_D_KM, !first);
+      gemm_km_t<8>(tmem + C_DQU, aT, aWb, ID_D_KM, !first);
       mma_commit(&bar_x1);
       gemm_mm_t<8>(tmem + C_X3, aT, aQu, ID_D_MM, false);
       mma_commit(&bar_x2);
