@@ -383,10 +383,10 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
   uint8_t* sG = smem;              // 16-bit copy of G (kept across steps)
   uint8_t* sA = sG + kSlot;        // Ku[I] -> gate A -> Qu[K]
   uint8_t* s0 = sA + kSlot;        // Qu[K] -> Kc[K] -> dT -> dqu staging
-  uint8_t* s1 = s0 + kSlot;        // Vu[I] -> dvu / dku staging
+  uint8_t* s1 = s0 + kSlot;        // Vu[I] -> Ku[I] -> dvu / dku staging
   uint8_t* s2 = s1 + kSlot;        // Qc[I] -> dvu / dku staging
   uint8_t* s3 = s2 + kSlot;        // dO[I] -> masked T -> dZ
-  uint8_t* s4 = s3 + kSlot;        // Vc[K] -> Wb -> dSu -> Ku[I] -> dqu staging
+  uint8_t* s4 = s3 + kSlot;        // Vc[K] -> Wb -> dSu -> dqu staging
   __shared__ uint64_t bar_a, bar_v, bar_kc, bar_ku2, bar_qu2, bar_mma;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
@@ -582,14 +582,14 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       mbar_expect_tx(&bar_ku2, kSlot);   // armed here; the loads are issued below by two other lanes
       if (!first) gemm_kk_t<2>(tmem + C_S, aG, a1, ID_KK, false);
       gemm_mm_t<8>(tmem + C_S, a4, a3, ID_MM, !first);
-      gemm_mm_t<8>(tmem + C_G, a4, a2, ID_MM, !first);
       gemm_km_t<8>(tmem + C_X, a4, aA, ID_KM, false);
-      mma_commit(&bar_mma);
+      mma_commit(&bar_mma);  // dA and dT: the pass below overlaps the G update, which the next commit covers
+      gemm_mm_t<8>(tmem + C_G, a4, a2, ID_MM, !first);
     }
     B128_MMA_WAIT();
     B128_MARK(256, 11);
-    // dSu is consumed: Ku[I] -> s4 for the dqu product
-    if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s4 + (warp == 9) * kPanelB, &m_ku, &bar_ku2, (warp == 9) * 64, i0, h, b);
+    // Vu[I] is consumed (dSu is not yet: the G update still reads it): Ku[I] -> s1 for the dqu product
+    if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s1 + (warp == 9) * kPanelB, &m_ku, &bar_ku2, (warp == 9) * 64, i0, h, b);
     {  // dZ = dA A (1 - A) -> s3 (over the masked T); masked dT -> s0 (over Kc)
       float v[32], a[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -614,7 +614,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       if (!first) gemm_mm_t<8>(tmem + C_X, aA, aG, ID_MM, false);
       gemm_mm_t<8>(tmem + C_X, a0, a2, ID_MM, !first);
       mbar_wait(&bar_ku2, ph_ku2, abortp);
-      gemm_km_t<8>(tmem + C_S, a3, a4, ID_KM, false);
+      gemm_km_t<8>(tmem + C_S, a3, a1, ID_KM, false);
       mma_commit(&bar_mma);
     }
     ph_ku2 ^= 1;
