@@ -468,19 +468,17 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       tc_fence_after();
       mbar_expect_tx(&bar_kc, kSlot);   // armed here; the loads are issued below by two other lanes
       gemm_kk_t<2>(tmem + C_S, a0, aA, ID_KK, false);
+      mma_commit(&bar_mma);   // Z alone: the gate pass overlaps the dP product, which the next commit covers
       gemm_kk_t<2>(tmem + C_X, a3, a4, ID_KK, false);
-      mma_commit(&bar_mma);
     }
     ph_a ^= 1;
     B128_MMA_WAIT();
     B128_MARK(256, 3);
     // Qu is consumed: Kc[K] -> s0
     if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s0 + (warp == 9) * kPanelB, &m_kc, &bar_kc, (warp == 9) * 64, k0, h, b);
-    float dpv[32];  // dP of this thread's 32 entries, kept until dS is formed
     {
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
-      tmem_ld32(trow + C_X + c0, dpv);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = sigmoid_t<T>(v[j] * p.scale);
@@ -503,9 +501,11 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     B128_MMA_WAIT();
     B128_MARK(256, 5);
+    float dpv[32];  // dP of this thread's 32 entries, kept until dS is formed
     {  // masked T -> s3 (over dO); 16-bit copy of the peeled state -> s4 (over Vc)
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
+      tmem_ld32(trow + C_X + c0, dpv);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;

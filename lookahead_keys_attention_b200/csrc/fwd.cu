@@ -65,7 +65,10 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   constexpr uint32_t OPB = NP * kPanelBytes;         // bytes of a d-wide operand tile
   constexpr uint32_t SQB = 2 * kPanelBytes;          // bytes of a 128x128 tile
   constexpr uint32_t TM_COLS = (D == 64) ? 256 : 512;
-  constexpr uint32_t COL_W = 0, COL_S = D, COL_O = D + 128;
+  static_assert(D == 128, "laid out for dim_head 128 (512 tensor-memory columns)");
+  // accumulators W | S | O, then two 64-column areas for tiles the threads hand to the tensor cores as
+  // packed 16-bit pairs (first operands read from tensor memory): the gate, later P; and the masked T
+  constexpr uint32_t COL_W = 0, COL_S = D, COL_O = D + 128, COL_A = D + 256, COL_T = D + 320;
   constexpr int FMT = Elem<T>::fmt;
   constexpr uint32_t ID_SQ = make_idesc(128, 128, FMT, false, false, false);
   constexpr uint32_t ID_D = make_idesc(128, D, FMT, false, true, false);
@@ -79,7 +82,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   uint8_t* sQc = sVc + OPB;
   uint8_t* sWb = sQc + OPB;
   uint8_t* sKuA = sWb + OPB;   // Ku[I], then the gate A[K,I]; Ku[I+1] arrives once Su is done
-  uint8_t* sVuT = sKuA + SQB;  // Vu[I], then the masked T[I,I], then the soft-max numerators P
+  uint8_t* sVuT = sKuA + SQB;  // Vu[I]; Vu[I+1] arrives once Su (whose commit covers the state update) is done
   // row max / row sum exchange between the four threads of a row: 4 KB over Qc[I], which is dead
   // once the last product reading it (Sc) has completed and until the next step's TMA load
   float (*red_max)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sQc);
@@ -179,8 +182,10 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = (c0 + j > row) ? v[j] : 0.f;
       }
-      store_row32<T>(sKuA, kPanelBytes, row, c0, v);
+      store_row32<T>(sKuA, kPanelBytes, row, c0, v);   // operand of the Su correction (read along rows)
+      tmem_st_packed32<T>(trow + COL_A + c0 / 2, v);   // first operand of the state update
     }
+    tmem_st_wait();
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -191,9 +196,9 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mbar_wait(&bar_vu, ph_load, abortp);
       mbar_wait(&bar_qc, ph_load, abortp);
       tc_fence_after();
-      gemm_km_t<8>(tmem + COL_W, aKuA, aVuT, ID_D, !diag);
       gemm_kk_t<NP>(tmem + COL_S, aQc, aVuT, ID_SQ, false);
-      mma_commit(&bar_mma);
+      mma_commit(&bar_mma);   // T alone: masking it overlaps the state update, which the next commit covers
+      gemm_tm_t<8>(tmem + COL_W, tmem + COL_A, aVuT, ID_D, !diag);
     }
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
@@ -205,9 +210,9 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
-      store_row32<T>(sVuT, kPanelBytes, row, c0, v);
+      tmem_st_packed32<T>(trow + COL_T + c0 / 2, v);   // first operand of the Su correction
     }
-    fence_async_smem();
+    tmem_st_wait();
     tc_fence_before();
     __syncthreads();
     PHASE_MARK(5);
@@ -215,18 +220,20 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     // ---- Su/scale = Qc[I] @ Wb^T + Tm @ A^T   (Wb = 16-bit copy of W before this step's update)
     if (tid == 0) {
       tc_fence_after();
-      if (more) mbar_expect_tx(&bar_ku, OPB);   // armed here; the loads are issued below by other lanes
+      if (more) { mbar_expect_tx(&bar_ku, OPB); mbar_expect_tx(&bar_vu, OPB); }   // loads issued below by other lanes
       if (!diag) gemm_kk_t<NP>(tmem + COL_S, aQc, aWb, ID_SQ, false);
-      gemm_kk_t<2>(tmem + COL_S, aVuT, aKuA, ID_SQ, !diag);
+      gemm_tk_t<2>(tmem + COL_S, tmem + COL_T, aKuA, ID_SQ, !diag);
       mma_commit(&bar_mma);
     }
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
     PHASE_MARK(6);
-    // the gate and the masked T are consumed: Ku[I+1] -> the gate's slot (P will go over the masked T)
+    // the gate, and Vu[I] with the state update, are consumed: Ku[I+1] and Vu[I+1] -> their slots
     if (more && lane == 0 && warp >= 4 && warp < 4 + NP)
       tma_load_4d(sKuA + (warp - 4) * kPanelBytes, &m_ku, &bar_ku, (warp - 4) * 64, in0, h, b);
+    if (more && lane == 0 && warp >= 8 && warp < 8 + NP)
+      tma_load_4d(sVuT + (warp - 8) * kPanelBytes, &m_vu, &bar_vu, (warp - 8) * 64, in0, h, b);
     {  // penalty -silu(Su)/scale goes back into the accumulator; Sc is then accumulated on top of it
       float v[32];
       tmem_ld32(trow + COL_S + c0, v);
@@ -287,8 +294,9 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
         v[j] = pe;
       }
       red_sum[cc][row] = lsum;
-      store_row32<T>(sVuT, kPanelBytes, row, c0, v);
+      tmem_st_packed32<T>(trow + COL_A + c0 / 2, v);   // P over the gate's packed copy, first operand of P @ Vc
     }
+    tmem_st_wait();
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -297,8 +305,8 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     // ---- O_partial = P @ Vc[K]
     if (tid == 0) {
       tc_fence_after();
-      if (more) { mbar_expect_tx(&bar_vu, OPB); mbar_expect_tx(&bar_qc, OPB); }   // loads issued by other lanes
-      gemm_km_t<8>(tmem + COL_O, aVuT, aVc, ID_D, false);
+      if (more) mbar_expect_tx(&bar_qc, OPB);   // the load is issued at the top of the next step
+      gemm_tm_t<8>(tmem + COL_O, tmem + COL_A, aVc, ID_D, false);
       mma_commit(&bar_mma);
     }
     const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;
@@ -311,9 +319,6 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     ph_mma ^= 1;
     tc_fence_after();
     PHASE_MARK(10);
-    // P is consumed: Vu[I+1] -> its slot
-    if (more && lane == 0 && warp >= 8 && warp < 8 + NP)
-      tma_load_4d(sVuT + (warp - 8) * kPanelBytes, &m_vu, &bar_vu, (warp - 8) * 64, in0, h, b);
     if (c0 < D) {
       uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.part_o) + (tile * kBlk + row) * D + c0);
       float v[32];
