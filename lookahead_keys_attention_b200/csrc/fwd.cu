@@ -196,17 +196,20 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       mbar_wait(&bar_vu, ph_load, abortp);
       mbar_wait(&bar_qc, ph_load, abortp);
       tc_fence_after();
-      gemm_kk_t<NP>(tmem + COL_S, aQc, aVuT, ID_SQ, false);
-      mma_commit(&bar_mma);   // T alone: masking it overlaps the state update, which the next commit covers
+      // T goes into O's columns (free until P @ Vc) and is committed alone: masking it overlaps the state
+      // update and the part of Su that does not need the masked T, which the next commit covers
+      gemm_kk_t<NP>(tmem + COL_O, aQc, aVuT, ID_SQ, false);
+      mma_commit(&bar_mma);
       gemm_tm_t<8>(tmem + COL_W, tmem + COL_A, aVuT, ID_D, !diag);
+      if (!diag) gemm_kk_t<NP>(tmem + COL_S, aQc, aWb, ID_SQ, false);
     }
     mbar_wait(&bar_mma, ph_mma, abortp);
     ph_mma ^= 1;
     tc_fence_after();
     PHASE_MARK(4);
-    {  // masked T (j <= i), unscaled, written over Vu[I]
+    {  // masked T (j <= i), unscaled
       float v[32];
-      tmem_ld32(trow + COL_S + c0, v);
+      tmem_ld32(trow + COL_O + c0, v);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : 0.f;
@@ -221,7 +224,6 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     if (tid == 0) {
       tc_fence_after();
       if (more) { mbar_expect_tx(&bar_ku, OPB); mbar_expect_tx(&bar_vu, OPB); }   // loads issued below by other lanes
-      if (!diag) gemm_kk_t<NP>(tmem + COL_S, aQc, aWb, ID_SQ, false);
       gemm_tk_t<2>(tmem + COL_S, tmem + COL_T, aKuA, ID_SQ, !diag);
       mma_commit(&bar_mma);
     }
