@@ -225,6 +225,9 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       tc_fence_after();
       if (more) { mbar_expect_tx(&bar_ku, OPB); mbar_expect_tx(&bar_vu, OPB); }   // loads issued below by other lanes
       gemm_tk_t<2>(tmem + COL_S, tmem + COL_T, aKuA, ID_SQ, !diag);
+      // the causal score Sc/scale = Qc[I] @ Kc[K]^T beside it, in O's columns (the masked T is consumed, P @ Vc
+      // comes later): one pass then forms S = Sc - silu(Su) and the soft-max numerators
+      gemm_kk_t<NP>(tmem + COL_O, aQc, aKc, ID_SQ, false);
       mma_commit(&bar_mma);
     }
     mbar_wait(&bar_mma, ph_mma, abortp);
@@ -236,46 +239,23 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       tma_load_4d(sKuA + (warp - 4) * kPanelBytes, &m_ku, &bar_ku, (warp - 4) * 64, in0, h, b);
     if (more && lane == 0 && warp >= 8 && warp < 8 + NP)
       tma_load_4d(sVuT + (warp - 8) * kPanelBytes, &m_vu, &bar_vu, (warp - 8) * 64, in0, h, b);
-    {  // penalty -silu(Su)/scale goes back into the accumulator; Sc is then accumulated on top of it
-      float v[32];
-      tmem_ld32(trow + COL_S + c0, v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float su = v[j] * p.scale;
-        v[j] = -v[j] * sigmoid_t<T>(su);   // = -silu(su) / scale
-      }
-      tmem_st32(trow + COL_S + c0, v);
-    }
     if (c0 < D) {  // refresh the 16-bit copy of W (now including block I) for the next step
       float v[32];
       tmem_ld32(trow + COL_W + c0, v);
       tmem_ld_wait();
       store_row32<T>(sWb, kPanelBytes, row, c0, v);
     }
-    tmem_st_wait();
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    PHASE_MARK(7);
-
-    // ---- S/scale = penalty + Qc[I] @ Kc[K]^T
-    if (tid == 0) {
-      tc_fence_after();
-      gemm_kk_t<NP>(tmem + COL_S, aQc, aKc, ID_SQ, true);
-      mma_commit(&bar_mma);
-    }
-    mbar_wait(&bar_mma, ph_mma, abortp);
-    ph_mma ^= 1;
-    tc_fence_after();
-    PHASE_MARK(8);
-    // row max over the four column chunks, then P = exp(S - max) (rows = queries i, columns = keys k)
+    // S/scale = Sc/scale - silu(Su)/scale, row max over the four column chunks, then P = exp(S - max)
+    // (rows = queries i, columns = keys k)
     const int irow = i0 + row;
     float mrow;
     {
-      float v[32];
-      tmem_ld32(trow + COL_S + c0, v);
+      float v[32], w[32];
+      tmem_ld32(trow + COL_S + c0, w);
+      tmem_ld32(trow + COL_O + c0, v);
       tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = fmaf(-w[j], sigmoid_t<T>(w[j] * p.scale), v[j]);
       if (diag) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = (c0 + j <= row) ? v[j] : -INFINITY;
