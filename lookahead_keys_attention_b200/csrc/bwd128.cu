@@ -136,15 +136,18 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     const float lse_b = rvalid ? p.lse[(int64_t)bh * p.N + irow] * kLog2e : 0.f;
     const float delta_i = rvalid ? p.delta[(int64_t)bh * p.N + irow] : 0.f;
 
+    B128_MARK(0, 0);
     // ---- M0: Z = Qu[K] @ Ku[I]^T
     if (tid == 0) {
       mbar_wait(&bar_a, ph_a, abortp);
+      B128_MARK(0, 1);
       tc_fence_after();
       gemm_kk_t<2>(tmem + C_S, a0, a1, ID_KK, false);
       mma_commit(&bar_mma);
     }
     ph_a ^= 1;
     B128_MMA_WAIT();
+    B128_MARK(0, 2);
     {  // gate A -> s1 (over Ku)
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -159,6 +162,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     if (issuer) bulk_wait_read0();  // this lane's dqc panel of the step before (in s5|s6) has been read
     B128_SYNC();
+    B128_MARK(0, 3);
 
     // ---- M1: peel W -= A @ Vu[I];  T = Qc[I] @ Vu[I]^T
     if (tid == 0) {
@@ -171,6 +175,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       load_tile<2>(s6, &m_do, &bar_b, i0, h, b);
     }
     B128_MMA_WAIT();
+    B128_MARK(0, 4);
     {  // masked T -> s2 (over Vu); 16-bit copy of the peeled state -> s0 (over Qu)
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -183,6 +188,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       store_row32<T>(s0, kPanelB, row, c0, v);
     }
     B128_SYNC();
+    B128_MARK(0, 5);
 
     // ---- M2: Su/scale = Qc[I] @ Wb^T + Tm @ A^T
     if (tid == 0) {
@@ -192,6 +198,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       mma_commit(&bar_mma);
     }
     B128_MMA_WAIT();
+    B128_MARK(0, 6);
     uint32_t dpk[16], ppk[16];
     {
       float v[32];
@@ -210,6 +217,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     tc_fence_before();
     __syncthreads();
+    B128_MARK(0, 7);
 
     // ---- M3: S/scale = penalty + Qc[I] @ Kc[K]^T
     if (tid == 0) {
@@ -218,6 +226,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       mma_commit(&bar_mma);
     }
     B128_MMA_WAIT();
+    B128_MARK(0, 8);
     {  // P -> s2 (over the masked T)
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -237,6 +246,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       store_row32<T>(s2, kPanelB, row, c0, v);
     }
     B128_SYNC();
+    B128_MARK(0, 9);
 
     // ---- M4: dvc += P^T @ dO[I];  dP = dO[I] @ Vc[K]^T
     if (tid == 0) {
@@ -249,6 +259,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     ph_b ^= 1;
     B128_MMA_WAIT();
+    B128_MARK(0, 10);
     // P is consumed: Vu[I] comes back into s2 for the last product (one panel per lane: a TMA
     // instruction costs its issuing thread ~150 cycles)
     if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s2 + (warp == 9) * kPanelB, &m_vu, &bar_vu2, (warp == 9) * 64, i0, h, b);
@@ -268,6 +279,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       store_row32<T>(s6, kPanelB, row, c0, w);
     }
     B128_SYNC();
+    B128_MARK(0, 11);
 
     // ---- M5: dkc += dS^T @ Qc[I];  dT = dSu @ A
     if (tid == 0) {
@@ -277,6 +289,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       gemm_mm_t<8>(tmem + C_DKC, a5, a3, ID_MM, !first);
     }
     B128_MMA_WAIT();
+    B128_MARK(0, 12);
     {  // masked dT -> s1 (over the gate)
       float v[32];
       tmem_ld32(trow + C_S + c0, v);
@@ -286,6 +299,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       store_row32<T>(s1, kPanelB, row, c0, v);
     }
     B128_SYNC();
+    B128_MARK(0, 13);
 
     // ---- M6: dqc[I] (unscaled) = dT @ Vu[I] + dSu @ Wb + dS @ Kc[K]
     // Three commits, in the order in which the products free the per-step slots, so that the next
@@ -313,6 +327,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     ph_x ^= 1;
     B128_MMA_WAIT();
+    B128_MARK(0, 14);
     {  // stage dqc[I] as four fp32 panels over s5|s6 and add it to the workspace by TMA reduce:
        // chunk group cc stages panel cc and one of its lanes issues that panel's reduce
       float v[32];
@@ -328,6 +343,7 @@ castle_bwd128_kv_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     tc_fence_before();
     __syncthreads();
+    B128_MARK(0, 15);
   }
   if (issuer) bulk_wait0();
 

@@ -24,6 +24,10 @@ PHASES = ["wait for Qc/Vu/Ku", "MMA Z", "gate A", "MMA peel, T", "masked T, Wb",
           "end barrier"]
 
 
+KV_PHASES = ["wait for Qu, Ku, Vu, Qc (fetched in the step before)", "MMA Z", "gate A (+ drain wait of the dqc reduce)",
+             "MMA peel, T", "masked T, Wb", "MMA Su", "penalty", "MMA Sc", "P", "MMA dvc, dP (+ wait Vc, dO)", "dS, dSu",
+             "MMA dT (+ dkc behind)", "masked dT", "MMA dqc (3 commits, + wait Vu)", "stage dqc, issue reduces, end barrier"]
+
 LA_PHASES = ["(issuing lanes refill the dku staging panels with Vu, Qc)", "wait for Qu, Ku, dO, Vc (fetched in the step before)",
              "MMA Z, dP", "gate A", "MMA peel, T", "masked T, Wb", "MMA Su", "penalty", "MMA Sc (+ wait Kc)",
              "P, dS, dSu", "MMA dA, G, dT", "dZ, masked dT", "MMA dvu, dqu part (+ wait Ku)",
@@ -97,6 +101,12 @@ def main():
     torch.cuda.synchronize()
     print(f"castle_bwd (all four launches, timing build {' '.join(extra)}): {e0.elapsed_time(e1) / 5:.3f} ms per call")
     if d == 128:
+        raw = ws[need:need + 8 * 32 * 8].view(torch.int64).cpu().view(8, 32)[1:7, :16]
+        dt = (raw[:, 1:] - raw[:, :-1]).double().mean(0)
+        print(f"castle_bwd128_kv_kernel<bf16>  B={B} H={H} N={N}: cycles per phase, CTA (0,0), mean of tile steps 1-6")
+        for name, c in zip(KV_PHASES, dt.tolist()):
+            print(f"  {name:44s} {c:8.0f}")
+        print(f"  {'total':44s} {dt.sum().item():8.0f}")
         raw = ws[need + 2048:need + 2048 + 8 * 32 * 8].view(torch.int64).cpu().view(8, 32)[1:7, :17]
         dt = (raw[:, 1:] - raw[:, :-1]).double().mean(0)
         print(f"castle_bwd128_la_kernel<bf16>  B={B} H={H} N={N}: cycles per phase, CTA (0,0), mean of tile steps 1-6")
