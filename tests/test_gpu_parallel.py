@@ -68,15 +68,17 @@ def test_forward_matches_reference_golden(name):
     _close(U.float().cpu(), gU, 3e-3 + 2 * 2.0 ** -11 * gU.abs().max().item(), 3e-3, "U vs reference")
 
 
-def test_forward_fp32_caller_atol_1e3():
-    """fp32 caller (the README shape's head geometry): atol 1e-3 against the fp32 oracle."""
+@pytest.mark.parametrize("B,H,N,d", [(2, 8, 128, 64), (1, 2, 300, 64), (1, 2, 300, 128)])
+def test_forward_fp32_caller_atol_1e3(B, H, N, d):
+    """fp32 caller (first case: the README shape's head geometry): atol 1e-3 against the fp32 oracle, for both
+    forward kernels and more than one key block."""
     from lookahead_keys_attention_b200 import castle_attention
-    packed = _inputs(2, 8, 128, 64, torch.float32, seed=7) * 0.5
+    packed = _inputs(B, H, N, d, torch.float32, seed=7) * 0.5
     qu, ku, vu, qc, kc, vc = _views(packed.cuda())
-    out = castle_attention(qc, kc, vc, qu, ku, vu, 0.125, False)
+    out = castle_attention(qc, kc, vc, qu, ku, vu, d ** -0.5, False)
     assert out.dtype == torch.float32
     rqu, rku, rvu, rqc, rkc, rvc = _views(packed)
-    ro = O.castle_parallel(rqc, rkc, rvc, rqu, rku, rvu, 0.125)
+    ro = O.castle_parallel(rqc, rkc, rvc, rqu, rku, rvu, d ** -0.5)
     _close(out.cpu(), ro, 1e-3, 0.0, "out")
 
 
