@@ -126,3 +126,25 @@ def test_repeatability_config2():
             assert torch.equal(g[:, :, slot], res[0][2][:, :, slot])
         # dqc, dku, dvu are fp32 sums in arrival order: equal up to a few bf16 ulps of the result
         assert torch.allclose(g.float(), res[0][2].float(), atol=3e-2, rtol=3e-2)
+
+
+def test_repeatability_d128():
+    """Same at dim_head 128 (its three kernels hand tiles over in tensor memory and refill shared-memory
+    panels lane by lane): out, U, dkc and dvc bit for bit; dqc, dqu, dku, dvu are fp32 sums in arrival order."""
+    from lookahead_keys_attention_b200 import castle_attention_packed, check_status
+    packed = _packed(1, 4096, 8, 128, seed=22)
+    gen = torch.Generator(device="cuda").manual_seed(6)
+    gout = torch.randn(1, 8, 4096, 128, device="cuda", generator=gen).bfloat16()
+    res = []
+    for _ in range(4):
+        p = packed.clone().requires_grad_()
+        out, U = castle_attention_packed(p, 128 ** -0.5, True)
+        out.backward(gout)
+        res.append((out.detach().clone(), U.clone(), p.grad.clone()))
+    torch.cuda.synchronize()
+    check_status()
+    for out, U, g in res[1:]:
+        assert torch.equal(out, res[0][0]) and torch.equal(U, res[0][1])
+        for slot in (4, 5):  # dkc, dvc
+            assert torch.equal(g[:, :, slot], res[0][2][:, :, slot])
+        assert torch.allclose(g.float(), res[0][2].float(), atol=3e-2, rtol=3e-2)
