@@ -87,7 +87,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   // once the last product reading it (Sc) has completed and until the next step's TMA load
   float (*red_max)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sQc);
   float (*red_sum)[kBlk] = reinterpret_cast<float (*)[kBlk]>(sQc + 4 * kBlk * sizeof(float));
-  __shared__ uint64_t bar_res, bar_ku, bar_vu, bar_qc, bar_mma;
+  __shared__ uint64_t bar_res, bar_ku, bar_vu, bar_qc, bar_mma, bar_z;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -104,6 +104,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     mbar_init(&bar_ku, 1);
     mbar_init(&bar_vu, 1);
     mbar_init(&bar_qc, 1);
+    mbar_init(&bar_z, 1);
     mbar_init(&bar_mma, 1);
     mbar_fence_init();
     abort_flag = 0;
@@ -139,7 +140,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
   }
   mbar_wait(&bar_res, 0, abortp);
 
-  uint32_t ph_load = 0, ph_mma = 0;
+  uint32_t ph_load = 0, ph_mma = 0, ph_z = 0;
   const uint32_t aQu = smem_u32(sQu), aKc = smem_u32(sKc), aVc = smem_u32(sVc), aQc = smem_u32(sQc),
                  aWb = smem_u32(sWb), aKuA = smem_u32(sKuA), aVuT = smem_u32(sVuT);
   const int krow = k0 + row;  // global key index of this thread's row when rows are keys
@@ -161,15 +162,21 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       tma_load_4d(sQc + (warp - 4) * kPanelBytes, &m_qc, &bar_qc, (warp - 4) * 64, i0, h, b);
 
     // ---- Z[K,I] = Qu[K] @ Ku[I]^T  (rows = keys k, columns = positions j)
-    if (tid == 0) {
-      mbar_wait(&bar_ku, ph_load, abortp);
-      PHASE_MARK(1);
-      tc_fence_after();
-      gemm_kk_t<NP>(tmem + COL_S, aQu, aKuA, ID_SQ, false);
-      mma_commit(&bar_mma);
+    // After the first step this product was already issued behind P @ Vc of the step before (see there).
+    if (diag) {
+      if (tid == 0) {
+        mbar_wait(&bar_ku, ph_load, abortp);
+        PHASE_MARK(1);
+        tc_fence_after();
+        gemm_kk_t<NP>(tmem + COL_S, aQu, aKuA, ID_SQ, false);
+        mma_commit(&bar_mma);
+      }
+      mbar_wait(&bar_mma, ph_mma, abortp);
+      ph_mma ^= 1;
+    } else {
+      mbar_wait(&bar_z, ph_z, abortp);
+      ph_z ^= 1;
     }
-    mbar_wait(&bar_mma, ph_mma, abortp);
-    ph_mma ^= 1;
     tc_fence_after();
     PHASE_MARK(2);
     {  // gate A = sigmoid(scale * Z), kept for j > k; written over Ku[I]
@@ -290,6 +297,12 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       if (more) mbar_expect_tx(&bar_qc, OPB);   // the load is issued at the top of the next step
       gemm_tm_t<8>(tmem + COL_O, tmem + COL_A, aVc, ID_D, false);
       mma_commit(&bar_mma);
+      if (more) {  // S is consumed and Ku[I+1] was fetched after the Su product: the next step's Z runs under the
+                   // store of this step's partial
+        mbar_wait(&bar_ku, ph_load ^ 1, abortp);
+        gemm_kk_t<NP>(tmem + COL_S, aQu, aKuA, ID_SQ, false);
+        mma_commit(&bar_z);
+      }
     }
     const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;
     if (cc == 0 && irow < p.N) {
