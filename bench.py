@@ -18,9 +18,11 @@ One step = forward + backward of the attention core.
             included.
   roofline  the backward main kernel alone, timed with CUDA events recorded around it.
   decode    (secondary) cached single-token decode at B=64, H=16, d=128, prefix 8192, 256 steps.
+  cfg4      (secondary) the long-context configuration's per-GPU slice: B=1, N=16384, H=32, d=128.
+  cfg3      (secondary, 1 GPU) training step of the 8-layer byte LM on batch 16 x 1024 bytes.
 
-`--impl reference` times the CPU oracle (a restatement of the reference's PyTorch path) on the
-host cores, on a bounded sample of the same workload.
+`--impl reference` times the reference's own PyTorch CPU path (its staged copy under oracle/_ref;
+the oracle port when that is absent) on the host cores, on a bounded sample of the same workload.
 """
 import argparse
 import json
@@ -45,6 +47,19 @@ def load_peaks():
         d = json.loads(p.read_text())
         return dict(tflops=float(d["bf16_tflops"]), hbm=float(d["hbm_gbs"]), source="measured")
     return dict(tflops=1590.0, hbm=6650.0, source="fallback")
+
+
+def captured_traffic(key, units):
+    """DRAM bytes per launch from the ncu summary table under profiles/, scaled to `units` of this launch
+    (None when no capture of that kernel and size is on file)."""
+    f = ROOT / "profiles" / "ncu_dram_traffic.txt"
+    if not f.exists():
+        return None
+    for ln in f.read_text().splitlines():
+        w = ln.split()
+        if len(w) >= 3 and w[0] == key:
+            return int(float(w[1]) / float(w[2]) * units)
+    return None
 
 
 def core_flops(b, h, n, d):
@@ -312,9 +327,8 @@ def run_ours(args):
                     "bwd_main_ms": round(bwd_ms, 4), "bwd_main_tflops": round(bwd_tflops, 2)},
         "roofline": {"kernel": "castle_bwd_kernel", "bound": "tensor", "achieved": round(bwd_tflops, 2),
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": round(bwd_tflops / peaks["tflops"], 4),
-                     # dram read+write bytes per launch: ncu capture of the B=2 case (1.052 GB), which grows
-                     # in proportion to the (batch, head) pairs a launch processes
-                     "traffic": int(1.052e9 / 32 * bs * hs) if (N, d) == (4096, 64) else None,
+                     "traffic": captured_traffic(f"bwd_d{d}_N{N}", bs * hs),
+                     "traffic_source": "profiles/ncu_dram_traffic.txt (ncu capture of a smaller launch, scaled by batch*head pairs)",
                      "peak_source": f"{peaks['source']} bf16 burst"},
         "clocks": clocks.summary(),
     }
@@ -326,11 +340,140 @@ def run_ours(args):
         dec = run_decode(args, world, rank, dev, peaks)
         if rank == 0:
             line["decode"] = dec
+    if not args.no_extra:
+        c4 = run_cfg4(world, dev, peaks)
+        if rank == 0:
+            line["cfg4"] = c4
+        if world == 1:
+            line["cfg3"] = run_cfg3(dev)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
+
+
+CFG4 = dict(batch=1, seq_len=16384, heads=32, dim_head=128, dim=4096, warmup=3, steps=5)
+CFG3 = dict(layers=8, dim=512, heads=8, dim_head=64, batch=16, seq_len=1024, warmup=3, steps=5)
+
+
+def run_cfg4(world, dev, peaks):
+    """Long-context configuration (B=8, N=16384, H=32, d_head=128 over 8 GPUs): every rank runs ONE per-GPU
+    slice (B=1, all 32 heads) of it, forward + backward of the core on the packed projection output."""
+    from lookahead_keys_attention_b200 import _lib, castle_attention_packed, check_status, release_workspaces
+    lib = _lib.load()
+    c = CFG4
+    B, N, H, d, dim = (c[k] for k in ("batch", "seq_len", "heads", "dim_head", "dim"))
+    gen = torch.Generator(dev).manual_seed(11)
+    with torch.no_grad():
+        w = torch.empty(6 * H * d, dim, device=dev).uniform_(-dim ** -0.5, dim ** -0.5, generator=gen).bfloat16()
+        x = torch.randn(B, N, dim, device=dev, generator=gen).bfloat16()
+        packed = (x @ w.T).view(B, N, 6, H, d)
+        del w, x
+    packed.requires_grad_()
+    g = torch.randn(B, N, H, d, device=dev, generator=gen).bfloat16().permute(0, 2, 1, 3)
+    scale = d ** -0.5
+
+    def step():
+        packed.grad = None
+        castle_attention_packed(packed, scale, False).backward(g)
+
+    for _ in range(c["warmup"]):
+        step()
+    torch.cuda.synchronize()
+    check_status()
+    n = c["steps"]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n)]
+    for row in ev:
+        for e in row:
+            e.record()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    e0.record()
+    for s_ in range(n):
+        lib.castle_set_kernel_events(0, ev[s_][0].cuda_event, ev[s_][1].cuda_event)
+        lib.castle_set_kernel_events(1, ev[s_][2].cuda_event, ev[s_][3].cuda_event)
+        step()
+    e1.record()
+    barrier(world)
+    lib.castle_set_kernel_events(0, None, None)
+    lib.castle_set_kernel_events(1, None, None)
+    check_status()
+    ms = max_over_ranks(e0.elapsed_time(e1) / n, world)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / n
+    bwd_ms = sum(e[2].elapsed_time(e[3]) for e in ev) / n
+    f_fwd, f_bwd = core_flops(B, H, N, d)
+    tf = (f_fwd + f_bwd) * world / (ms * 1e-3) / 1e12
+    del packed, g
+    release_workspaces()
+    torch.cuda.empty_cache()
+    return {"metric": "castle_attn_fwd_bwd_tflops", "value": round(tf, 2), "unit": "TFLOP/s", "ms_per_step": round(ms, 3),
+            "steps": n, "warmup": c["warmup"],
+            "config": {"workload": f"long-context slice per GPU: B={B} N={N} H={H} d_head={d} (1/8 of B=8), forward+backward of the core",
+                       "slices": world},
+            "frac_of_tensor_peak": round(tf / (peaks["tflops"] * world), 4),
+            "kernels": {"fwd_main_ms": round(fwd_ms, 3), "fwd_main_tflops": round(f_fwd / (fwd_ms * 1e-3) / 1e12, 2),
+                        "bwd_main_ms": round(bwd_ms, 3), "bwd_main_tflops": round(f_bwd / (bwd_ms * 1e-3) / 1e12, 2)}}
+
+
+class ByteLM(torch.nn.Module):
+    """The model shape of the reference's training script (train_triton.py:73-175 there): byte embedding,
+    layers of [Castle(prenorm) + residual, RMSNorm -> 4x GELU FFN + residual], final RMSNorm, logits."""
+
+    def __init__(self, layers, dim, heads, dim_head):
+        from torch import nn
+        from lookahead_keys_attention_b200 import Castle
+        super().__init__()
+        self.emb = nn.Embedding(256, dim)
+        self.attn = nn.ModuleList([Castle(dim, heads=heads, dim_head=dim_head, prenorm=True) for _ in range(layers)])
+        self.ff = nn.ModuleList([nn.Sequential(nn.RMSNorm(dim), nn.Linear(dim, 4 * dim), nn.GELU(), nn.Linear(4 * dim, dim))
+                                 for _ in range(layers)])
+        self.norm = nn.RMSNorm(dim)
+        self.logits = nn.Linear(dim, 256, bias=False)
+
+    def forward(self, ids):
+        x, y = ids[:, :-1], ids[:, 1:]
+        h = self.emb(x)
+        for a, f in zip(self.attn, self.ff):
+            h = a(h) + h
+            h = f(h) + h
+        return torch.nn.functional.cross_entropy(self.logits(self.norm(h)).float().flatten(0, 1), y.flatten())
+
+
+def run_cfg3(dev):
+    """8-layer byte LM, bf16 training step (forward, backward, clip, Adam) on batch 16 x 1024 uniform bytes."""
+    from lookahead_keys_attention_b200 import check_status
+    c = CFG3
+    torch.manual_seed(5)
+    lm = ByteLM(c["layers"], c["dim"], c["heads"], c["dim_head"]).to(dev).bfloat16()
+    opt = torch.optim.Adam(lm.parameters(), lr=1e-4)
+    ids = torch.randint(0, 256, (c["batch"], c["seq_len"] + 1), device=dev)
+    losses = []
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        loss = lm(ids)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(lm.parameters(), 0.5)
+        opt.step()
+        losses.append(loss.detach())
+
+    for _ in range(c["warmup"]):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(c["steps"]):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    check_status()
+    ms = e0.elapsed_time(e1) / c["steps"]
+    return {"metric": "lm_train_tokens_per_s", "value": round(c["batch"] * c["seq_len"] / (ms * 1e-3), 1), "unit": "tokens/s",
+            "ms_per_step": round(ms, 3), "steps": c["steps"], "warmup": c["warmup"],
+            "loss_first_last": [round(float(losses[0]), 4), round(float(losses[-1]), 4)],
+            "config": {"workload": f"{c['layers']}-layer byte LM, dim {c['dim']}, {c['heads']} heads x {c['dim_head']}, pre-RMSNorm, 4x GELU FFN, "
+                                   f"batch {c['batch']} x {c['seq_len']} uniform bytes, bf16, Adam, clip 0.5 (one step = fwd + bwd + optimizer)"}}
 
 
 def run_decode(args, world, rank, dev, peaks):
@@ -361,8 +504,8 @@ def run_decode(args, world, rank, dev, peaks):
                 bufs[i][b0:b0 + n, :, :c["prefix"]].copy_(cb[i])
                 b0 += n
         del caches
-        from lookahead_keys_attention_b200 import Cache
-        cache = Cache(*(b[:, :, :c["prefix"]] for b in bufs))
+        from lookahead_keys_attention_b200 import cache_from_buffers
+        cache = cache_from_buffers(*bufs, length=c["prefix"])   # the module appends to these buffers in place
         xs = torch.randn(steps + warm, bs, 1, c["dim"], device=dev, generator=gen).bfloat16()
         for s in range(warm):
             _, cache = m(xs[s], cache=cache)
@@ -392,26 +535,52 @@ def run_decode(args, world, rank, dev, peaks):
                        "per_gpu_batch": bs},
             "roofline": {"kernel": "castle_decode_ring_kernel", "bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm"],
                          "unit": "GB/s", "frac": round(gbs / peaks["hbm"], 4),
-                         # ncu capture at B=8: dram read+write = 0.98 x the algorithmic bytes
-                         "traffic": int(alg_bytes * 0.98),
+                         "traffic": captured_traffic(f"decode_d{c['dim_head']}", alg_bytes),
                          "algorithmic_bytes_per_launch": int(alg_bytes), "peak_source": peaks["source"]}}
 
 
-# --------------------------------------------------------------------------- CPU oracle arm
+# --------------------------------------------------------------------------- CPU reference arm
+CPU_SAMPLE_HEADS = 2
+
+
 def cpu_sample_time(steps, warmup):
-    """Forward + backward of the oracle (the reference's PyTorch arithmetic, bf16) on a bounded
-    sample of the workload: 1 batch row x 2 heads at the full N=4096, d=64."""
-    from oracle import castle_oracle as O
-    N, d, hs = CFG["seq_len"], CFG["dim_head"], 2
+    """Forward + backward of the reference's own PyTorch path on the host cores, on a bounded sample
+    of the workload: 1 batch row x 2 heads at the full N=4096, d=64, bf16.
+
+    When the staged copy of the reference is present (oracle/_ref, made by oracle/make_ref.py) the
+    thing timed is the reference's `Castle(use_triton=False)` module, forward + AUTOGRAD backward
+    (lookahead_keys_attention.py:132-164), projections included; otherwise the oracle port (same
+    arithmetic, closed-form backward).  Either way the flops credited are the algorithmic 19u of the
+    sample's attention core."""
+    from oracle import make_ref
+    N, d, hs, dim = CFG["seq_len"], CFG["dim_head"], CPU_SAMPLE_HEADS, CFG["dim"]
+    torch.set_num_threads(os.cpu_count() or 1)   # launchers set OMP_NUM_THREADS=1; the baseline may use every core
     torch.manual_seed(0)
-    t = [(torch.randn(1, hs, N, d) * 3 ** -0.5).bfloat16() for _ in range(6)]
-    g = torch.randn(1, hs, N, d).bfloat16()
-    scale = d ** -0.5
+    if make_ref.available():
+        RefCastle = make_ref.load_reference()
+        m = RefCastle(dim, heads=hs, dim_head=d, use_triton=False).bfloat16()
+        x = torch.randn(1, N, dim).bfloat16().requires_grad_()
+        g = torch.randn(1, N, dim).bfloat16()
 
-    def step():
-        O.castle_parallel(*t, scale)
-        O.castle_parallel_bwd(*t, scale, g)
+        def step():
+            x.grad = None
+            m.zero_grad(set_to_none=True)
+            m(x).backward(g)
 
+        kind = "reference"
+        what = "the reference's Castle(use_triton=False) from oracle/_ref, forward + autograd backward, projections included"
+    else:
+        from oracle import castle_oracle as O
+        t = [(torch.randn(1, hs, N, d) * 3 ** -0.5).bfloat16() for _ in range(6)]
+        g = torch.randn(1, hs, N, d).bfloat16()
+        scale = d ** -0.5
+
+        def step():
+            O.castle_parallel(*t, scale)
+            O.castle_parallel_bwd(*t, scale, g)
+
+        kind = "port"
+        what = "oracle port (oracle/_ref not staged), forward + closed-form backward of the core"
     for _ in range(warmup):
         step()
     t0 = time.perf_counter()
@@ -419,12 +588,13 @@ def cpu_sample_time(steps, warmup):
         step()
     dt = (time.perf_counter() - t0) / steps
     f_fwd, f_bwd = core_flops(1, hs, N, d)
-    return dt, (f_fwd + f_bwd) / dt / 1e12, f"1 batch row x {hs} heads of the workload (N={N}, d={d}), bf16, oracle fwd + closed-form bwd"
+    sample = f"1 batch row x {hs} heads of the workload (N={N}, d={d}, dim={dim}), bf16: {what}"
+    return dt, (f_fwd + f_bwd) / dt / 1e12, sample, kind
 
 
 def cpu_baseline(steps, warmup):
-    dt, tf, sample = cpu_sample_time(steps, warmup)
-    return {"value": round(tf, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+    dt, tf, sample, kind = cpu_sample_time(steps, warmup)
+    return {"value": round(tf, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
             "sample": sample, "s_per_sample": round(dt, 3)}
 
 
@@ -432,15 +602,17 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warm = min(args.steps, 5), min(args.warmup, 1)
-    dt, tf, sample = cpu_sample_time(steps, warm)
+    steps, warm = args.steps, max(args.warmup, 1)
+    dt, tf, sample, kind = cpu_sample_time(steps, warm)
+    B, N, H, d, dim = (CFG[k] for k in ("batch", "seq_len", "heads", "dim_head", "dim"))
     line = {
         "impl": "reference", "metric": "castle_attn_fwd_bwd_tflops", "value": round(tf, 5), "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": round(dt * 1e3, 2),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "castle_attention_layer B=4 N=4096 H=16 d_head=64 dim=1024, forward+backward",
-                   "flops": "19*B*H*N^2*d algorithmic"},
-        "cpu_baseline": {"value": round(tf, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+        "config": {"workload": f"castle_attention_layer B={B} N={N} H={H} d_head={d} dim={dim}, forward+backward",
+                   "sample_per_step": f"1 batch row x {CPU_SAMPLE_HEADS} heads of the {B}x{H} (batch, head) pairs, at the full N",
+                   "flops": "19*B*H*N^2*d algorithmic, of the sample"},
+        "cpu_baseline": {"value": round(tf, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
                          "sample": sample},
         "e2e": {"value": round(tf, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -459,6 +631,7 @@ def main():
                     help="strong (default): the fixed B=4,H=16 problem is split over the GPUs, as the benchmark "
                          "configuration says; weak: every GPU runs the whole problem (global batch 4*N)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end arm (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the long-context slice and the LM step (profiling runs)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline (profiling runs)")
     ap.add_argument("--batch", type=int, default=None, help="override B (smaller case of the same workload, for ncu)")
     ap.add_argument("--seq-len", type=int, default=None, help="override N (for ncu captures)")

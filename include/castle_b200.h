@@ -77,6 +77,25 @@ int castle_fwd(const castle_problem_t* p, const castle_tensor_t* qc, const castl
                int32_t u_dtype, float* w_state, void* workspace, size_t workspace_bytes, int32_t* status,
                void* stream);
 
+/* ---- parallel forward that fills the decode caches (prefill) ---------------
+ * Replaces the cache hand-off of the reference's parallel branch
+ * (lookahead_keys_attention/lookahead_keys_attention.py:161-164: `U` plus the
+ * unscaled qu, kc, vc become `Cache(U, qu_cache, kc_cache, vc_cache)`, which
+ * the sampling loop of train_triton.py:113-139 then feeds token by token).
+ * Same computation as castle_fwd(); in addition rows [0, seq_len) of the four
+ * caches are written by the kernel itself: U from the final lookahead state,
+ * qu/kc/vc from the tiles each key-block CTA holds in shared memory, so the
+ * host needs no copy passes afterwards.  The caches are (batch, heads,
+ * capacity >= seq_len, dim_head) buffers of the problem's dtype, described
+ * with their own strides; rows at and beyond seq_len are left untouched.
+ */
+int castle_fwd_prefill(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
+                       const castle_tensor_t* vc, const castle_tensor_t* qu, const castle_tensor_t* ku,
+                       const castle_tensor_t* vu, const castle_tensor_t* out, float* lse,
+                       const castle_tensor_t* u_cache, const castle_tensor_t* qu_cache,
+                       const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache, float* w_state,
+                       void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
 /* ---- parallel backward ---------------------------------------------------
  * Replaces CastleAttentionFunction.backward
  * (lookahead_keys_attention_triton.py:509-602) with its two kernels
@@ -139,33 +158,6 @@ int castle_decode_step_static(const castle_problem_t* p, int32_t cache_len, int3
                               const castle_tensor_t* u_cache, const castle_tensor_t* qu_cache,
                               const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache,
                               const castle_tensor_t* out, int32_t* status, void* stream);
-
-/* ---- measurement aid ------------------------------------------------------
- * (no counterpart in the reference)  Bracket the MAIN kernel of later calls (from
- * any host thread of the process) with two caller-owned CUDA events recorded on the launch
- * stream: which = 0 forward, 1 backward, 2 decode step.  Pass NULL events to
- * stop.  Lets a benchmark time the dominant kernel alone, without a profiler.
- */
-enum { CASTLE_KERNEL_FWD = 0, CASTLE_KERNEL_BWD = 1, CASTLE_KERNEL_DECODE = 2 };
-int castle_set_kernel_events(int32_t which, void* start_event, void* stop_event);
-
-/* ---- self test -------------------------------------------------------------
- * Runs one 128x128 tensor-core product through each operand form the kernels
- * use (no counterpart in the reference).  `x`, `y`: bf16 [128][128] device
- * buffers; `d`: fp32 [128][128].  mode 0: d = x @ y^T; 1: d = x @ y;
- * 2: d = x^T @ y; 3: d = x^T @ y^T; 4: d = 1 - x @ y^T (preset accumulator,
- * negated operand); 5..8: as 0..3 with operands staged by TMA instead of
- * thread stores; 9: d = x @ y^T and 10: d = x @ y with x read from tensor
- * memory (packed 16-bit pairs) instead of shared memory.
- */
-int castle_selftest_mma(int32_t mode, const void* x, const void* y, float* d, int32_t* status, void* stream);
-
-/* Measurement aid (no counterpart in the reference): `reps` back-to-back 128 x n x 16 tensor-core
- * products in one operand form (0: both operands read along rows, 1: B read down its columns,
- * 2: both read down their columns, 3: A read down its columns), n in {64, 128, 192, 256}.
- * cycles[0] = SM cycles spent issuing, cycles[1] = cycles from first issue to completion
- * (device pointer to two int64). */
-int castle_selftest_mma_rate(int32_t form, int32_t n, int32_t reps, long long* cycles, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

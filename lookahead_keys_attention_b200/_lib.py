@@ -40,27 +40,70 @@ def _sources():
     return [CSRC / s for s in SOURCES if (CSRC / s).exists()]
 
 
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+              "-Xcompiler", "-fPIC"]
+STAMP_PATH = PKG_DIR / "libcastle_b200.so.stamp"
+
+
+def _deps():
+    return sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list((PKG_DIR.parent / "include").glob("*.h")))
+
+
+def _source_hash() -> str:
+    """Digest of every source the library is built from plus the compiler flags.  Compared with
+    the stamp written next to the library, so a stale build is noticed whatever the file times say
+    (a copied tree does not keep them)."""
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for d in _deps():
+        h.update(d.name.encode())
+        h.update(d.read_bytes())
+    return h.hexdigest()
+
+
 def needs_build():
-    if not LIB_PATH.exists():
+    if not LIB_PATH.exists() or not STAMP_PATH.exists():
         return True
-    mt = LIB_PATH.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "castle_b200.h"]
-    return any(d.stat().st_mtime > mt for d in deps if d.exists())
+    return STAMP_PATH.read_text().strip() != _source_hash()
+
+
+def _locked(fn):
+    """Run `fn` holding the build lock (one builder per tree; ranks that start together queue here)."""
+    import fcntl
+    with open(PKG_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return fn()
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_unlocked(verbose: bool = False):
+    tmp = LIB_PATH.with_name(f".libcastle_b200.{os.getpid()}.tmp.so")
+    cmd = [_nvcc()] + NVCC_FLAGS + ["-Xptxas", "-v" if verbose else "-warn-spills", "-o", str(tmp)] + \
+          [str(s) for s in _sources()]
+    digest = _source_hash()
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+        os.replace(tmp, LIB_PATH)          # readers see the old library or the complete new one, never half of it
+        STAMP_PATH.write_text(digest + "\n")
+    finally:
+        if tmp.exists():
+            tmp.unlink()
+    if verbose:
+        print(res.stderr)
+    return LIB_PATH
 
 
 def build(force: bool = False, verbose: bool = False):
     """Compile every kernel for sm_100a into one shared library next to this file."""
-    if not force and not needs_build():
-        return LIB_PATH
-    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "-shared", "-Xcompiler", "-fPIC", "-Xptxas", "-v" if verbose else "-warn-spills",
-           "-o", str(LIB_PATH)] + [str(s) for s in _sources()]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        print(res.stderr)
-    return LIB_PATH
+    def go():
+        if not force and not needs_build():
+            return LIB_PATH
+        return _build_unlocked(verbose)
+    return _locked(go)
 
 
 _lib = None
@@ -74,6 +117,7 @@ _SIGNATURES = {
     "castle_last_error": (ctypes.c_char_p, []),
     "castle_fwd_workspace_bytes": (_sz, [_PR]),
     "castle_fwd": (ctypes.c_int, [_PR] + [_T] * 7 + [_vp, _T, _i32, _vp, _vp, _sz, _vp, _vp]),
+    "castle_fwd_prefill": (ctypes.c_int, [_PR] + [_T] * 7 + [_vp] + [_T] * 4 + [_vp, _vp, _sz, _vp, _vp]),
     "castle_bwd_workspace_bytes": (_sz, [_PR]),
     "castle_bwd": (ctypes.c_int, [_PR] + [_T] * 8 + [_vp, _vp] + [_T] * 6 + [_vp, _sz, _vp, _vp]),
     "castle_decode_workspace_bytes": (_sz, [_PR, _i32]),
@@ -82,6 +126,7 @@ _SIGNATURES = {
     "castle_set_kernel_events": (ctypes.c_int, [_i32, _vp, _vp]),
     "castle_selftest_mma_rate": (ctypes.c_int, [_i32, _i32, _i32, _vp, _vp, _vp]),
     "castle_selftest_mma": (ctypes.c_int, [_i32, _vp, _vp, _vp, _vp, _vp]),
+    "castle_selftest_wait_timeout": (ctypes.c_int, [_i32, _vp, _vp, _vp]),
 }
 
 
@@ -90,20 +135,17 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
-        # compile on demand (one process at a time); there is no other code path to fall back to
-        import fcntl
-        with open(PKG_DIR / ".build.lock", "w") as lock:
-            fcntl.flock(lock, fcntl.LOCK_EX)
+    def ensure():
+        # compile on demand when the library is missing or was built from other sources; there is
+        # no other code path to fall back to
+        if needs_build():
             try:
-                if not LIB_PATH.exists():
-                    build(force=True)
+                _build_unlocked()
             except Exception as e:
-                raise RuntimeError(f"{LIB_PATH} is missing and could not be built ({e}); run "
+                raise RuntimeError(f"{LIB_PATH} is missing or stale and could not be rebuilt ({e}); run "
                                    "`python -c 'import __graft_entry__ as g; g.build()'` where nvcc is "
                                    "available - this package has no fallback path") from e
-            finally:
-                fcntl.flock(lock, fcntl.LOCK_UN)
+    _locked(ensure)
     lib = ctypes.CDLL(str(LIB_PATH))
     for name, (res, args) in _SIGNATURES.items():
         fn = getattr(lib, name)

@@ -9,6 +9,7 @@
 #include <stdio.h>
 
 #include "../../include/castle_b200.h"
+#include "../../include/castle_b200_diag.h"
 
 namespace castle {
 

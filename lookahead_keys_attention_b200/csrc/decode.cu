@@ -9,6 +9,7 @@
 // Rows are split over `nsplit` CTAs per (batch, head); each CTA keeps a running
 // (max, sum, weighted value sum) and writes one partial, which a small second
 // kernel merges.
+#include <mutex>
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -308,13 +309,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 4) castle_decode_ring_kernel(c
   for (int tile = 0; tile < ntiles; ++tile) {
     const int st = tile % kRingStages;
     mbar_wait(&full[st], (uint32_t)((tile / kRingStages) & 1), abortp);
+    // A wait that ran out means this stage never arrived: the U cache is persistent state, so
+    // nothing computed from such a stage may be stored.  (No early exit: the barrier below must
+    // still be reached by every thread.)
+    const bool arrived = (*abortp == 0);
     const uint8_t* src = ring + (size_t)st * 4 * TENB;
     const int r0 = r_begin + tile * kRingRows;
 #pragma unroll
     for (int ps = 0; ps < PASSES; ++ps) {
       const int rr = ps * RPW * NW + warp * RPW + grp;   // row inside the tile
       const int r = r0 + rr;
-      const bool live = rr < kRingRows && r < r_end;
+      const bool live = arrived && rr < kRingRows && r < r_end;
       float quv[VEC], uv[VEC], kv[VEC], vv[VEC];
       if (live) {
         const T* base = reinterpret_cast<const T*>(src) + (size_t)rr * D + col;
@@ -362,7 +367,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 4) castle_decode_ring_kernel(c
     Vec<T>::load(row_ptr(p.qu, 0), qn);
 #pragma unroll
     for (int i = 0; i < VEC; ++i) zero[i] = 0.f;
-    if (grp == 0) {
+    if (grp == 0 && *abortp == 0) {   // a timed-out step leaves the caches as they were
       Vec<T>::store(row_ptr(p.kcc, p.t), kn);
       Vec<T>::store(row_ptr(p.vcc, p.t), vn);
       Vec<T>::store(row_ptr(p.quc, p.t), qn);
@@ -592,6 +597,7 @@ static __device__ __align__(256) float g_decode_static_scratch[kStaticMaxSlots *
 // use; the device address is looked up once per device and kept here.
 constexpr int kMaxDevices = 64;
 static float* g_decode_static_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_decode_static_mu;   // host threads may make their first call on a device at the same time
 
 }  // namespace castle
 
@@ -624,11 +630,16 @@ extern "C" int castle_decode_step_static(const castle_problem_t* p, int32_t cach
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e, "castle_decode_step_static cudaGetDevice");
   if (dev < 0 || dev >= kMaxDevices) return reject("castle_decode_step_static: device ordinal %d not supported", dev);
-  if (g_decode_static_ptr[dev] == nullptr) {
-    float* ptr = nullptr;
-    e = cudaGetSymbolAddress((void**)&ptr, g_decode_static_scratch);
-    if (e != cudaSuccess) return cuda_fail(e, "castle_decode_step_static cudaGetSymbolAddress");
-    g_decode_static_ptr[dev] = ptr;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_decode_static_mu);
+    if (g_decode_static_ptr[dev] == nullptr) {
+      float* ptr = nullptr;
+      e = cudaGetSymbolAddress((void**)&ptr, g_decode_static_scratch);
+      if (e != cudaSuccess) return cuda_fail(e, "castle_decode_step_static cudaGetSymbolAddress");
+      g_decode_static_ptr[dev] = ptr;
+    }
+    scratch = g_decode_static_ptr[dev];
   }
   DecodeParams dp;
   dp.qc = *qc_new; dp.kc = *kc_new; dp.vc = *vc_new; dp.qu = *qu_new; dp.ku = *ku_new; dp.vu = *vu_new;
@@ -639,7 +650,7 @@ extern "C" int castle_decode_step_static(const castle_problem_t* p, int32_t cach
   if (dp.rows_per_split < 1) dp.rows_per_split = 1;
   // Every partial slot the merge kernel reads is written by this same call first, so the
   // array needs no clearing between calls even though it keeps the previous call's contents.
-  dp.part = g_decode_static_ptr[dev];
+  dp.part = scratch;
   cudaStream_t st = (cudaStream_t)stream;
   switch (p->dtype) {
     case CASTLE_BF16: return launch_decode_d<__nv_bfloat16>(dp, BH, p->dim_head, false, st);

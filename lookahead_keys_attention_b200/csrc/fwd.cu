@@ -37,6 +37,7 @@ struct FwdParams {
   int u_dtype;
   castle_tensor_t out;
   int32_t* status;
+  int store_caches;   // also copy the Qu[K], Kc[K], Vc[K] tiles into the decode caches (prefill hand-off)
 #ifdef CASTLE_PHASE_TIMING
   long long* timing;
 #endif
@@ -60,7 +61,9 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
                   const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
-                  const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu) {
+                  const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu,
+                  const __grid_constant__ CUtensorMap m_quc, const __grid_constant__ CUtensorMap m_kcc,
+                  const __grid_constant__ CUtensorMap m_vcc) {
   constexpr int NP = D / 64;                         // panels per d-wide operand
   constexpr uint32_t OPB = NP * kPanelBytes;         // bytes of a d-wide operand tile
   constexpr uint32_t SQB = 2 * kPanelBytes;          // bytes of a 128x128 tile
@@ -139,6 +142,18 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
     }
   }
   mbar_wait(&bar_res, 0, abortp);
+  // Prefill hand-off: the resident tiles of this key block are exactly the rows the decode caches hold for
+  // it, so they go there straight from shared memory (the slots are never overwritten; the stores are
+  // awaited before the CTA exits).
+  if (p.store_caches && tid == 0 && !*abortp) {
+#pragma unroll
+    for (int pn = 0; pn < NP; ++pn) {
+      tma_store_4d(&m_quc, sQu + pn * kPanelBytes, pn * 64, k0, h, b);
+      tma_store_4d(&m_kcc, sKc + pn * kPanelBytes, pn * 64, k0, h, b);
+      tma_store_4d(&m_vcc, sVc + pn * kPanelBytes, pn * 64, k0, h, b);
+    }
+    bulk_commit();
+  }
 
   uint32_t ph_load = 0, ph_mma = 0, ph_z = 0;
   const uint32_t aQu = smem_u32(sQu), aKc = smem_u32(sKc), aVc = smem_u32(sVc), aQc = smem_u32(sQc),
@@ -373,6 +388,7 @@ castle_fwd_kernel(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, c
       }
     }
   }
+  if (p.store_caches && tid == 0) bulk_wait0();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TM_COLS);
@@ -405,7 +421,9 @@ template <typename T, int G>
 __global__ void __launch_bounds__(G * 128, 2)
 castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
                       const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
-                      const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu) {
+                      const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu,
+                      const __grid_constant__ CUtensorMap m_quc, const __grid_constant__ CUtensorMap m_kcc,
+                      const __grid_constant__ CUtensorMap m_vcc) {
   constexpr int D = 64;
   constexpr int NCH = 4 / G;   // 32-column chunks of a 128-column tile per thread
   constexpr uint32_t OPB = kPanelBytes;
@@ -469,6 +487,9 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
     mbar_expect_tx(bar_vu, OPB);
     tma_load_4d(sVuT, &m_vu, bar_vu, 0, k0, h, b);
     mbar_wait(bar_qu, 0, abortp);
+    // Prefill hand-off: Qu[K] is the block's rows of the decode cache; Kc[K] and Vc[K] follow in the
+    // first step, each when its fetch has landed (see there).
+    if (p.store_caches && !*abortp) tma_store_4d(&m_quc, sQu, 0, k0, h, b);
   }
 
   uint32_t ph_ld = 0, ph_mma = 0;   // all per-step load barriers flip once per step
@@ -587,6 +608,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       tc_fence_after();
       gemm_kk_t<1>(tmem + COL_S, aQV, aVuT, ID_SQ, true);
       mma_commit(bar_mma);
+      if (diag && p.store_caches && !*abortp) tma_store_4d(&m_kcc, sVuT, 0, k0, h, b);
     }
     F2_MMA_WAIT();
     PHASE_MARK(7);
@@ -643,6 +665,10 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       tc_fence_after();
       gemm_tm_t<8>(tmem + COL_O, tmem + COL_S, aQV, ID_D, false);
       mma_commit(bar_mma);
+      if (diag && p.store_caches) {
+        if (!*abortp) tma_store_4d(&m_vcc, sQV, 0, k0, h, b);
+        bulk_commit();
+      }
     }
     const int64_t tile = (int64_t)bh * tri(p.nblk) + tri(I) + K;
     if (grp == 0 && irow < p.N) {
@@ -657,6 +683,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
     PHASE_MARK(9);
     if (tid == 0 && !last) {  // every slot of this step is dead: fetch the next step's Qc, Ku, Vu
       const int in0 = i0 + kBlk;
+      if (diag && p.store_caches) bulk_wait_read0();   // the cache stores have read the Kc and Vc slots
       mbar_expect_tx(bar_qc, OPB);
       tma_load_4d(sQV, &m_qc, bar_qc, 0, in0, h, b);
       mbar_expect_tx(bar_ku, OPB);
@@ -725,6 +752,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       }
     }
   }
+  if (p.store_caches && tid == 0) bulk_wait0();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TM_COLS);
@@ -778,7 +806,8 @@ static int launch_fwd_d64(const FwdParams& p, const CUtensorMap* maps, cudaStrea
   }
   dim3 grid(p.B * p.H, p.nblk);
   ev_start(CASTLE_KERNEL_FWD, st);
-  castle_fwd_kernel_d64<T, G><<<grid, G * 128, kFwd2Smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+  castle_fwd_kernel_d64<T, G><<<grid, G * 128, kFwd2Smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+                                                                 maps[6], maps[7], maps[8]);
   ev_stop(CASTLE_KERNEL_FWD, st);
   constexpr int ROWS = 256 / (64 / 8);
   dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);
@@ -796,7 +825,8 @@ static int launch_fwd(const FwdParams& p, const CUtensorMap* maps, cudaStream_t 
   }
   dim3 grid(p.B * p.H, p.nblk);
   ev_start(CASTLE_KERNEL_FWD, st);
-  castle_fwd_kernel<T, D><<<grid, kFwdThreads, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+  castle_fwd_kernel<T, D><<<grid, kFwdThreads, smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+                                                            maps[6], maps[7], maps[8]);
   ev_stop(CASTLE_KERNEL_FWD, st);
   constexpr int ROWS = 256 / (D / 8);
   dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);
@@ -826,27 +856,31 @@ extern "C" size_t castle_fwd_workspace_bytes(const castle_problem_t* p) {
   return (size_t)(tiles * kBlk * (2 * sizeof(float) + p->dim_head * 2));  // (max, sum) fp32 + a 16-bit row
 }
 
-extern "C" int castle_fwd(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
-                          const castle_tensor_t* vc, const castle_tensor_t* qu, const castle_tensor_t* ku,
-                          const castle_tensor_t* vu, const castle_tensor_t* out, float* lse,
-                          const castle_tensor_t* u_out, int32_t u_dtype, float* w_state, void* workspace,
-                          size_t workspace_bytes, int32_t* status, void* stream) {
-  int rc = check_parallel_problem(p, "castle_fwd");
+static int fwd_impl(const char* who, const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
+                    const castle_tensor_t* vc, const castle_tensor_t* qu, const castle_tensor_t* ku,
+                    const castle_tensor_t* vu, const castle_tensor_t* out, float* lse, const castle_tensor_t* u_out,
+                    int32_t u_dtype, float* w_state, const castle_tensor_t* const* caches, void* workspace,
+                    size_t workspace_bytes, int32_t* status, void* stream) {
+  int rc = check_parallel_problem(p, who);
   if (rc) return rc;
   const castle_tensor_t* ins[6] = {qc, kc, vc, qu, ku, vu};
   const char* names[6] = {"qc", "kc", "vc", "qu", "ku", "vu"};
   for (int i = 0; i < 6; ++i)
     if (!tensor_ok(ins[i], p->dtype, names[i], &rc)) return rc;
   if (!tensor_ok(out, p->dtype, "out", &rc)) return rc;
-  if (!lse || !status) return reject("castle_fwd: lse and status must not be null");
+  if (!lse || !status) return reject("%s: lse and status must not be null", who);
   if (u_out && u_out->ptr) {
-    if (u_dtype != CASTLE_BF16 && u_dtype != CASTLE_F16 && u_dtype != CASTLE_F32) return reject("castle_fwd: bad u_dtype");
+    if (u_dtype != CASTLE_BF16 && u_dtype != CASTLE_F16 && u_dtype != CASTLE_F32) return reject("%s: bad u_dtype", who);
     if (!tensor_ok(u_out, u_dtype, "u_out", &rc)) return rc;
   }
+  const char* cnames[3] = {"qu_cache", "kc_cache", "vc_cache"};
+  if (caches)
+    for (int i = 0; i < 3; ++i)
+      if (!tensor_ok(caches[i], p->dtype, cnames[i], &rc)) return rc;
   size_t need = castle_fwd_workspace_bytes(p);
   if (!workspace || workspace_bytes < need)
-    return reject("castle_fwd: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
-  if (((uintptr_t)workspace) % 16) return reject("castle_fwd: workspace not 16-byte aligned");
+    return reject("%s: workspace too small (%zu < %zu bytes)", who, workspace_bytes, need);
+  if (((uintptr_t)workspace) % 16) return reject("%s: workspace not 16-byte aligned", who);
 
   FwdParams fp;
   fp.B = p->batch; fp.H = p->heads; fp.N = p->seq_len; fp.nblk = (p->seq_len + kBlk - 1) / kBlk;
@@ -858,17 +892,46 @@ extern "C" int castle_fwd(const castle_problem_t* p, const castle_tensor_t* qc, 
   fp.u_out = (u_out && u_out->ptr) ? *u_out : castle_tensor_t{nullptr, 0, 0, 0};
   fp.u_dtype = u_dtype;
   fp.out = *out; fp.status = status;
+  fp.store_caches = caches ? 1 : 0;
 #ifdef CASTLE_PHASE_TIMING
   fp.timing = (long long*)((char*)workspace + need);  // the caller leaves 1 KB beyond the partials
 #endif
 
-  CUtensorMap maps[6];
+  CUtensorMap maps[9];
   for (int i = 0; i < 6; ++i) {
     rc = make_tmap_16bit(&maps[i], ins[i], p->dtype, p->batch, p->heads, p->seq_len, p->dim_head, kBlk, names[i]);
+    if (rc) return rc;
+  }
+  for (int i = 0; i < 3; ++i) {
+    // without caches the three maps are never used by the kernel; give them a valid encoding anyway
+    const castle_tensor_t* t = caches ? caches[i] : ins[3];
+    rc = make_tmap_16bit(&maps[6 + i], t, p->dtype, p->batch, p->heads, p->seq_len, p->dim_head, kBlk, cnames[i]);
     if (rc) return rc;
   }
   cudaStream_t st = (cudaStream_t)stream;
   if (p->dtype == CASTLE_BF16)
     return p->dim_head == 64 ? launch_fwd_d64<__nv_bfloat16>(fp, maps, st) : launch_fwd<__nv_bfloat16, 128>(fp, maps, st);
   return p->dim_head == 64 ? launch_fwd_d64<__half>(fp, maps, st) : launch_fwd<__half, 128>(fp, maps, st);
+}
+
+extern "C" int castle_fwd(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
+                          const castle_tensor_t* vc, const castle_tensor_t* qu, const castle_tensor_t* ku,
+                          const castle_tensor_t* vu, const castle_tensor_t* out, float* lse,
+                          const castle_tensor_t* u_out, int32_t u_dtype, float* w_state, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream) {
+  return fwd_impl("castle_fwd", p, qc, kc, vc, qu, ku, vu, out, lse, u_out, u_dtype, w_state, nullptr, workspace,
+                  workspace_bytes, status, stream);
+}
+
+extern "C" int castle_fwd_prefill(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
+                                  const castle_tensor_t* vc, const castle_tensor_t* qu, const castle_tensor_t* ku,
+                                  const castle_tensor_t* vu, const castle_tensor_t* out, float* lse,
+                                  const castle_tensor_t* u_cache, const castle_tensor_t* qu_cache,
+                                  const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache, float* w_state,
+                                  void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  if (!u_cache || !u_cache->ptr || !qu_cache || !kc_cache || !vc_cache)
+    return reject("castle_fwd_prefill: the four cache tensors must not be null");
+  const castle_tensor_t* caches[3] = {qu_cache, kc_cache, vc_cache};
+  return fwd_impl("castle_fwd_prefill", p, qc, kc, vc, qu, ku, vu, out, lse, u_cache, p ? p->dtype : 0, w_state, caches,
+                  workspace, workspace_bytes, status, stream);
 }

@@ -191,3 +191,38 @@ extern "C" int castle_selftest_mma_rate(int32_t form, int32_t n, int32_t reps, l
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : cuda_fail(e, "castle_selftest_mma_rate launch");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Failure path of the bounded waits, exercised without faulting anything: 128 threads allocate
+// tensor memory like a production CTA, then ALL wait on an mbarrier nothing arrives on.  The first
+// thread whose polls run out raises the abort flag; the others see it and return; a second wait
+// must then return at once; the CTA frees its tensor memory and reports through the status word.
+namespace castle {
+__global__ void __launch_bounds__(128) castle_wait_timeout_kernel(uint32_t poll_limit, int32_t* polls, int32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); abort_flag = 0; }
+  if (warp == 0) { tmem_alloc(&tmem_base_s, 32); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t n1 = mbar_wait(&bar, 0, &abort_flag, poll_limit);   // never completes: gives up after poll_limit polls
+  const uint32_t n2 = mbar_wait(&bar, 0, &abort_flag, poll_limit);   // the flag is up: returns at the first poll
+  if (tid == 0) { polls[0] = (int32_t)n1; polls[1] = (int32_t)n2; }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 32);
+  if (tid == 0 && abort_flag) atomicOr(status, CASTLE_STATUS_WAIT_TIMEOUT);
+}
+}  // namespace castle
+
+extern "C" int castle_selftest_wait_timeout(int32_t poll_limit, int32_t* polls, int32_t* status, void* stream) {
+  if (poll_limit < 1 || poll_limit > 65536) return reject("castle_selftest_wait_timeout: poll_limit must be 1..65536");
+  if (!polls || !status) return reject("castle_selftest_wait_timeout: null pointer");
+  castle_wait_timeout_kernel<<<1, 128, 0, (cudaStream_t)stream>>>((uint32_t)poll_limit, polls, status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : cuda_fail(e, "castle_selftest_wait_timeout launch");
+}

@@ -46,13 +46,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kWaitPollLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return;
-    if (*abort_flag) return;
+// Bounded wait.  `abort_flag` lives in shared memory and is shared by the CTA.  Returns the number of
+// polls made (the production kernels ignore it; the failure-path self test reports it).
+__device__ __forceinline__ uint32_t mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              uint32_t poll_limit = kWaitPollLimit) {
+  for (uint32_t i = 0; i < poll_limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return i;
+    if (*abort_flag) return i;
   }
   *abort_flag = 1;
+  return poll_limit;
 }
 
 // Barrier over the 128 threads (four warps) of one chunk group; ids 1..15 (0 is __syncthreads).
@@ -85,6 +88,13 @@ __device__ __forceinline__ void tma_reduce_add_3d(const void* tmap, const void* 
 __device__ __forceinline__ void tma_store_3d(const void* tmap, const void* src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap),
                "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+// 4-D tile store from a swizzled shared-memory tile (what tma_load_4d wrote) to global memory; rows of the
+// tile that fall outside the tensor are dropped.  Joins the thread's bulk async-group.
+__device__ __forceinline__ void tma_store_4d(const void* tmap, const void* src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tmap),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }

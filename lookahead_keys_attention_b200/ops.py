@@ -51,13 +51,22 @@ def check_status(device=None):
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
-    """Grow-only scratch buffer per (device, stream)."""
+    """Scratch buffer per (device, stream), grown on demand and kept between calls (kernels of
+    one stream run in order, so they can share it; two streams must not).  `release_workspaces()`
+    gives the memory back."""
     key = (torch.device(device), torch.cuda.current_stream(device).cuda_stream)
     w = _workspaces.get(key)
     if w is None or w.numel() < nbytes:
+        _workspaces.pop(key, None)   # drop the old buffer before allocating the larger one
+        w = None
         w = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = w
     return w
+
+
+def release_workspaces():
+    """Free every cached scratch buffer (they are re-created on the next call)."""
+    _workspaces.clear()
 
 
 def _desc(t: torch.Tensor) -> CastleTensor:
@@ -78,19 +87,47 @@ def _stream(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
-# bounded scratch per launch: the forward's soft-max partials grow with N^2/128 per (batch, head)
+# Bound on the forward's scratch per launch.  The soft-max partials take N^2/128 * (8 + 2*d) bytes
+# per (batch, head) pair (O(N^2), where the reference kernel needs O(N*d)), so a call is cut into
+# launches over whole batch rows, or over head ranges of one batch row, that each stay below it.
 MAX_WORKSPACE_BYTES = 8 << 30
+
+
+def forward_chunks(B: int, H: int, per_pair: int, limit: int | None = None):
+    """Rectangles (b0, b1, h0, h1) of the (batch, head) grid, each needing at most `limit` bytes of
+    scratch at `per_pair` bytes per pair.  A rectangle spans several batch rows only with all heads,
+    so that the per-pair fp32 buffers (lse, state) of a rectangle stay contiguous."""
+    limit = MAX_WORKSPACE_BYTES if limit is None else limit
+    pairs = limit // max(per_pair, 1)
+    if pairs < 1:
+        raise RuntimeError(f"castle_attention: one (batch, head) pair needs {per_pair} bytes of forward scratch, "
+                           f"more than the {limit}-byte bound (sequence too long for this build)")
+    def even(total, most):   # cut `total` into the fewest pieces of at most `most`, all about the same size
+        n = -(-total // most)
+        size = -(-total // n)
+        return [(i, min(total, i + size)) for i in range(0, total, size)]
+
+    if pairs >= H:
+        return [(b0, b1, 0, H) for b0, b1 in even(B, min(B, pairs // H))]
+    return [(b, b + 1, h0, h1) for b in range(B) for h0, h1 in even(H, pairs)]
+
+
+def prefill_writes_caches(dtype: torch.dtype, d: int) -> bool:
+    """Whether the forward kernels can fill the decode caches themselves: they store their 16-bit
+    operand tiles, so the caller's dtype must be the compute dtype and dim_head a tile width."""
+    return dtype in (torch.bfloat16, torch.float16) and d in (64, 128)
 
 
 class _CastleAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U):
+    def forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, cache_out=None):
         return _CastleAttention.run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U,
-                                            any(ctx.needs_input_grad[:6]))
+                                            any(ctx.needs_input_grad[:6]), cache_out)
 
     @staticmethod
-    def run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, need_grad):
-        """Shared by the six-view and the packed operator; `need_grad` says whether to save state."""
+    def run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, need_grad, cache_out=None):
+        """Shared by the six-view and the packed operator; `need_grad` says whether to save state.
+        `cache_out` = four (B, H, N, d) views of decode-cache buffers the kernels fill (prefill)."""
         _require_cuda(qc, "castle_attention")
         lib = _lib.load()
         B, H, N, d = qc.shape
@@ -101,6 +138,12 @@ class _CastleAttention(torch.autograd.Function):
         dp = 64 if d <= 64 else 128
         if d > 128 or d % 8:
             raise RuntimeError(f"castle_attention: dim_head {d} not supported (multiples of 8 up to 128)")
+        if cache_out is not None:
+            if not (return_U and prefill_writes_caches(orig_dtype, d)):
+                raise RuntimeError("castle_attention: cache_out needs return_U, a 16-bit dtype and dim_head 64 or 128")
+            for c in cache_out:
+                if c.shape != (B, H, N, d) or c.dtype != orig_dtype or c.stride(3) != 1:
+                    raise RuntimeError("castle_attention: cache_out tensors must be (B, H, N, d) views in the input dtype")
 
         def prep(t):
             if t.dtype != cdtype:
@@ -114,24 +157,33 @@ class _CastleAttention(torch.autograd.Function):
         # laid out (B, N, H, d): merging heads afterwards is a free reshape
         out = torch.empty(B, N, H, dp, dtype=cdtype, device=dev).permute(0, 2, 1, 3)
         lse = torch.empty(B, H, N, dtype=torch.float32, device=dev)
-        U = torch.empty(B, H, N, dp, dtype=orig_dtype, device=dev) if return_U else None
+        if cache_out is not None:
+            U = cache_out[0]
+        else:
+            U = torch.empty(B, H, N, dp, dtype=orig_dtype, device=dev) if return_U else None
         wst = torch.empty(B, H, N, dp, dtype=torch.float32, device=dev) if need_grad else None
         st = status_word(dev)
-        # chunk over batch so the partial-softmax scratch stays bounded
-        prob1 = CastleProblem(1, H, N, dp, _DTYPES[cdtype], float(scale))
-        per_b = max(int(lib.castle_fwd_workspace_bytes(ctypes.byref(prob1))), 1)
-        bchunk = max(1, min(B, MAX_WORKSPACE_BYTES // per_b))
-        ws = _workspace(dev, per_b * bchunk)
-        for b0 in range(0, B, bchunk):
-            b1 = min(B, b0 + bchunk)
-            prob = CastleProblem(b1 - b0, H, N, dp, _DTYPES[cdtype], float(scale))
-            d6 = [_desc(t[b0:b1]) for t in ins]
-            do = _desc(out[b0:b1])
-            du = _desc(U[b0:b1]) if return_U else None
+        # cut the (batch, head) grid so the partial-softmax scratch of one launch stays bounded
+        prob1 = CastleProblem(1, 1, N, dp, _DTYPES[cdtype], float(scale))
+        per_pair = max(int(lib.castle_fwd_workspace_bytes(ctypes.byref(prob1))), 1)
+        chunks = forward_chunks(B, H, per_pair)
+        ws = _workspace(dev, max(per_pair * (b1 - b0) * (h1 - h0) for b0, b1, h0, h1 in chunks))
+        for b0, b1, h0, h1 in chunks:
+            prob = CastleProblem(b1 - b0, h1 - h0, N, dp, _DTYPES[cdtype], float(scale))
+            d6 = [_desc(t[b0:b1, h0:h1]) for t in ins]
+            do = _desc(out[b0:b1, h0:h1])
+            wptr = wst[b0:b1, h0:h1].data_ptr() if need_grad else None
+            if cache_out is not None:
+                dc = [_desc(c[b0:b1, h0:h1]) for c in cache_out]
+                rc = lib.castle_fwd_prefill(ctypes.byref(prob), *[ctypes.byref(x) for x in d6], ctypes.byref(do),
+                                            lse[b0:b1, h0:h1].data_ptr(), *[ctypes.byref(x) for x in dc], wptr,
+                                            ws.data_ptr(), ws.numel(), st.data_ptr(), _stream(dev))
+                _lib.check(rc, "castle_fwd_prefill")
+                continue
+            du = _desc(U[b0:b1, h0:h1]) if return_U else None
             rc = lib.castle_fwd(ctypes.byref(prob), *[ctypes.byref(x) for x in d6], ctypes.byref(do),
-                                lse[b0:b1].data_ptr(), ctypes.byref(du) if return_U else None,
-                                _DTYPES[orig_dtype], wst[b0:b1].data_ptr() if need_grad else None,
-                                ws.data_ptr(), ws.numel(), st.data_ptr(), _stream(dev))
+                                lse[b0:b1, h0:h1].data_ptr(), ctypes.byref(du) if return_U else None,
+                                _DTYPES[orig_dtype], wptr, ws.data_ptr(), ws.numel(), st.data_ptr(), _stream(dev))
             _lib.check(rc, "castle_fwd")
         if need_grad:
             ctx.save_for_backward(*ins, out, lse, wst)
@@ -140,8 +192,9 @@ class _CastleAttention(torch.autograd.Function):
         if orig_dtype != cdtype:
             o = o.to(orig_dtype)
         if return_U:
+            U = U[..., :d]
             ctx.mark_non_differentiable(U)
-            return o, U[..., :d]
+            return o, U
         return o
 
     @staticmethod
@@ -173,7 +226,7 @@ class _CastleAttention(torch.autograd.Function):
         res = [g[..., :d] for g in (gqc, gkc, gvc, gqu, gku, gvu)]
         if ctx.orig_dtype != cdtype:
             res = [g.to(ctx.orig_dtype) for g in res]
-        return (*res, None, None)
+        return (*res, None, None, None)
 
 
 class _CastleAttentionPacked(torch.autograd.Function):
@@ -182,25 +235,28 @@ class _CastleAttentionPacked(torch.autograd.Function):
     autograd has nothing to scatter or sum (six separate view-gradients cost ~10 extra passes)."""
 
     @staticmethod
-    def forward(ctx, packed, scale, return_U):
+    def forward(ctx, packed, scale, return_U, cache_out=None):
         qu, ku, vu, qc, kc, vc = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(6))
-        return _CastleAttention.run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, ctx.needs_input_grad[0])
+        return _CastleAttention.run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, ctx.needs_input_grad[0],
+                                            cache_out)
 
     @staticmethod
     def backward(ctx, do, dU=None):
-        return _CastleAttention.backward(ctx, do, dU, packed_out=True), None, None
+        return _CastleAttention.backward(ctx, do, dU, packed_out=True), None, None, None
 
 
-def castle_attention_packed(packed, scale, return_U_for_cache=False):
+def castle_attention_packed(packed, scale, return_U_for_cache=False, cache_out=None):
     """Parallel CASTLE attention on the packed projection output (B, N, 6, H, d), order
-    qu,ku,vu,qc,kc,vc (the layout `to_all_qkv` produces).  Returns out (B, H, N, d) [, U]."""
-    return _CastleAttentionPacked.apply(packed, scale, bool(return_U_for_cache))
+    qu,ku,vu,qc,kc,vc (the layout `to_all_qkv` produces).  Returns out (B, H, N, d) [, U].
+    With `cache_out` = four (B, H, N, d) views (U, qu, kc, vc) of decode-cache buffers, the
+    kernels write the cache rows themselves and the returned U is cache_out[0]."""
+    return _CastleAttentionPacked.apply(packed, scale, bool(return_U_for_cache), cache_out)
 
 
-def castle_attention(qc, kc, vc, qu, ku, vu, scale, return_U_for_cache=False):
+def castle_attention(qc, kc, vc, qu, ku, vu, scale, return_U_for_cache=False, cache_out=None):
     """Parallel CASTLE attention on (B, H, N, d) tensors (views are fine).
-    Returns `out`, or `(out, U)` when `return_U_for_cache`."""
-    return _CastleAttention.apply(qc, kc, vc, qu, ku, vu, scale, bool(return_U_for_cache))
+    Returns `out`, or `(out, U)` when `return_U_for_cache`; `cache_out` as in `castle_attention_packed`."""
+    return _CastleAttention.apply(qc, kc, vc, qu, ku, vu, scale, bool(return_U_for_cache), cache_out)
 
 
 def castle_decode_step(qc, kc, vc, qu, ku, vu, U, qu_cache, kc_cache, vc_cache, cache_len: int, scale: float):

@@ -36,8 +36,13 @@ def test_mma_rate_runs_and_is_sane(form, n):
     """The rate micro-benchmark finishes with a clean status and a plausible cost per instruction
     (a 128 x n x 16 product cannot beat n/2 cycles on this part, and 4x that would mean a broken loop)."""
     from lookahead_keys_attention_b200 import _lib
-    from lookahead_keys_attention_b200.mma_rate import measure
     lib = _lib.load()
+
+    def measure(lib, form, n, reps, cyc, st):
+        _lib.check(lib.castle_selftest_mma_rate(form, n, reps, cyc.data_ptr(), st.data_ptr(), None), "mma_rate")
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        return cyc.cpu().tolist()
     cyc = torch.zeros(2, dtype=torch.int64, device="cuda")
     st = torch.zeros(1, dtype=torch.int32, device="cuda")
     _, t1 = measure(lib, form, n, 32, cyc, st)

@@ -155,12 +155,84 @@ def test_module_cache_regrows_when_capacity_runs_out():
     assert torch.allclose(torch.cat(outs, 1), m(x), atol=1e-3)
 
 
-def test_forward_batch_chunking_of_scratch(monkeypatch):
-    """The forward's partial-soft-max scratch is bounded by processing the batch in chunks."""
+def test_forward_chunking_of_scratch(monkeypatch):
+    """The forward's partial-soft-max scratch is bounded by cutting the (batch, head) grid into
+    launches: whole batch rows when they fit, head ranges of one batch row when they do not."""
     from lookahead_keys_attention_b200 import castle_attention_packed, ops
     torch.manual_seed(6)
-    packed = (torch.randn(3, 300, 6, 2, 64, device="cuda") * 0.5).bfloat16()
+    packed = (torch.randn(3, 300, 6, 4, 64, device="cuda") * 0.5).bfloat16().requires_grad_()
+    g = torch.randn(3, 4, 300, 64, device="cuda").bfloat16()
     ref, ref_u = castle_attention_packed(packed, 0.125, True)
-    monkeypatch.setattr(ops, "MAX_WORKSPACE_BYTES", 1)  # forces one batch row per launch
-    out, u = castle_attention_packed(packed, 0.125, True)
-    assert torch.equal(out, ref) and torch.equal(u, ref_u)
+    ref.backward(g)
+    ref_grad, packed.grad = packed.grad, None
+    per_pair = 6 * 128 * (8 + 2 * 64)          # 3 query blocks -> 6 tiles of (max, sum) + a 16-bit row
+    for limit in (4 * per_pair, 3 * per_pair, per_pair):   # one batch row; 3 + 1 heads; one pair per launch
+        monkeypatch.setattr(ops, "MAX_WORKSPACE_BYTES", limit)
+        out, u = castle_attention_packed(packed, 0.125, True)
+        assert torch.equal(out, ref) and torch.equal(u, ref_u)
+        out.backward(g)   # the saved per-pair state of a head-chunked forward feeds the backward as usual
+        assert torch.allclose(packed.grad.float(), ref_grad.float(), atol=3e-2, rtol=3e-2)
+        packed.grad = None
+    monkeypatch.setattr(ops, "MAX_WORKSPACE_BYTES", per_pair - 1)
+    with pytest.raises(RuntimeError, match="more than"):
+        castle_attention_packed(packed, 0.125, True)
+
+
+@torch.no_grad()
+@pytest.mark.parametrize("d,rotary", [(64, False), (128, False), (64, True)])
+def test_prefill_kernels_write_the_decode_caches(d, rotary, monkeypatch):
+    """Prefill hand-off (reference: lookahead_keys_attention.py:161-164): for 16-bit modules the forward
+    kernels fill all four caches themselves - U from the final lookahead state, qu/kc/vc from the tiles
+    in shared memory - straight into the capacity buffers; the module makes no copy pass."""
+    from lookahead_keys_attention_b200 import Castle, ModuleCache
+    torch.manual_seed(7)
+    H, N = 3, 333      # 333 rows: the last key block is ragged, rows beyond N must stay untouched
+    m = Castle(96, heads=H, dim_head=d, rotary_emb=rotary).cuda().bfloat16()
+    x = torch.randn(2, N, 96, device="cuda").bfloat16()
+    copies = []
+    real_copy = torch.Tensor.copy_
+    monkeypatch.setattr(torch.Tensor, "copy_", lambda self, *a, **k: (copies.append(self.shape), real_copy(self, *a, **k))[1])
+    out, cache = m(x, return_next_cache=True)
+    monkeypatch.setattr(torch.Tensor, "copy_", real_copy)
+    assert not copies, f"prefill made copy passes: {copies}"
+    assert isinstance(cache, ModuleCache) and cache.is_current()
+    bufs = cache._state.bufs
+    for c, b in zip(cache, bufs):
+        assert c.data_ptr() == b.data_ptr() and c.shape == (2, H, N, d) and b.shape[2] > N
+    qu, ku, vu, qc, kc, vc = m._split(m.to_all_qkv(x))
+    if rotary:
+        qc, kc, qu, ku, vu = (m.rotary_emb.rotate(t, 0) for t in (qc, kc, qu, ku, vu))
+    assert torch.equal(cache.qu_cache, qu) and torch.equal(cache.kc_cache, kc) and torch.equal(cache.vc_cache, vc)
+    ref_u = O.castle_parallel(*[t.float().cpu() for t in (qc, kc, vc, qu, ku, vu)], m.scale, return_U=True)[1]
+    err = (cache.U.float().cpu() - ref_u).abs()
+    assert bool((err <= 2e-2 + 1e-2 * ref_u.abs()).all()), err.max().item()
+    # and the hand-off works: cached steps continue the sequence
+    x2 = torch.randn(2, 3, 96, device="cuda").bfloat16()
+    full = m(torch.cat((x, x2), 1))
+    for t in range(3):
+        o, cache = m(x2[:, t:t + 1], cache=cache)
+        assert torch.allclose(o.float(), full[:, N + t:N + t + 1].float(), atol=2e-2, rtol=2e-2)
+
+
+@torch.no_grad()
+def test_decode_never_writes_a_callers_tensor():
+    """A cache made of the caller's own tensors (here: prefix slices of larger tensors, which look just
+    like capacity buffers) is copied before the in-place step; the caller's memory stays as it was, and
+    decoding twice from it gives the same answer."""
+    from lookahead_keys_attention_b200 import Cache, Castle
+    torch.manual_seed(8)
+    m = Castle(64, heads=2, dim_head=64).cuda().bfloat16()
+    big = [torch.randn(2, 2, 10, 64, device="cuda").bfloat16() for _ in range(4)]
+    keep = [b.clone() for b in big]
+    foreign = Cache(*(b[:, :, :4] for b in big))
+    x = torch.randn(2, 1, 64, device="cuda").bfloat16()
+    o1, c1 = m(x, cache=foreign)
+    o2, c2 = m(x, cache=foreign)
+    torch.cuda.synchronize()
+    assert all(torch.equal(b, k) for b, k in zip(big, keep))
+    assert torch.equal(o1, o2) and c1.U.data_ptr() != c2.U.data_ptr() and c1.U.data_ptr() != big[0].data_ptr()
+    # a stale module cache is refused rather than silently decoded from rewritten rows
+    _, c3 = m(x, cache=c1)
+    with pytest.raises(RuntimeError, match="advanced in place"):
+        m(x, cache=c1)
+    assert c3.is_current()

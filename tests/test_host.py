@@ -19,12 +19,15 @@ def _lib():
 def test_library_exports_every_declared_symbol():
     L = _lib()
     lib = L.load()
-    header = (ROOT / "include" / "castle_b200.h").read_text()
-    code = re.sub(r"/\*.*?\*/", "", header, flags=re.S)  # declarations only, not the comments
-    names = set(re.findall(r"\b(castle_[a-z0-9_]+)\s*\(", code))
-    assert {"castle_fwd", "castle_bwd", "castle_decode_step", "castle_abi_version"} <= names
-    for n in names:
-        assert hasattr(lib, n), f"{n} declared in include/castle_b200.h but not exported"
+    names = set()
+    for header in sorted((ROOT / "include").glob("*.h")):
+        code = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)  # declarations only, not the comments
+        found = set(re.findall(r"\b(castle_[a-z0-9_]+)\s*\(", code))
+        for n in found:
+            assert hasattr(lib, n), f"{n} declared in include/{header.name} but not exported"
+        names |= found
+    assert {"castle_fwd", "castle_bwd", "castle_decode_step", "castle_abi_version",
+            "castle_selftest_wait_timeout"} <= names
     assert lib.castle_abi_version() == 1
 
 
@@ -72,16 +75,59 @@ def test_partition_covers_grid_once():
         partition(3, 5, 2, 0)
 
 
-def test_capacity_view_roundtrip():
-    from lookahead_keys_attention_b200.castle import _capacity_view
-    for B, H in [(2, 3), (1, 3), (2, 1), (1, 1)]:
-        buf = torch.arange(B * H * 10 * 8, dtype=torch.float32).view(B, H, 10, 8)
-        v = _capacity_view(buf[:, :, :4])
-        assert v is not None and v.shape == (B, H, 10, 8) and v.data_ptr() == buf.data_ptr()
-        assert torch.equal(v, buf)
-    assert _capacity_view(torch.zeros(2, 3, 4, 8)) is None           # no spare rows
-    assert _capacity_view(torch.zeros(2, 3, 0, 8)) is None           # empty cache
-    assert _capacity_view(torch.zeros(2, 4, 3, 8).transpose(1, 2)) is None
+def test_cache_ownership_is_explicit():
+    """Only caches the module made (or was handed through cache_from_buffers) are updated in place;
+    tensors of the caller are copied, never written; a stale cache is refused."""
+    from lookahead_keys_attention_b200 import Cache, Castle, ModuleCache, cache_from_buffers
+    m = Castle(32, heads=3, dim_head=8, cache_headroom=4)
+    like = torch.zeros(2, 3, 1, 8)
+    # (1) a prefix slice of a caller tensor looks like a buffer with spare rows - it must be copied
+    big = [torch.arange(2 * 3 * 10 * 8, dtype=torch.float32).view(2, 3, 10, 8) + i for i in range(4)]
+    keep = [b.clone() for b in big]
+    foreign = Cache(*(b[:, :, :4] for b in big))
+    st = m._buffers_for_step(foreign, 4, like)
+    assert all(buf.data_ptr() != b.data_ptr() for buf, b in zip(st.bufs, big))
+    assert all(torch.equal(buf[:, :, :4], b[:, :, :4]) for buf, b in zip(st.bufs, big))
+    for buf in st.bufs:
+        buf.fill_(-1.0)                      # whatever the step writes ...
+    assert all(torch.equal(b, k) for b, k in zip(big, keep))   # ... the caller's memory is untouched
+    # (2) a cache of the module: in place while it is the latest one
+    own = ModuleCache(st, 4)
+    assert isinstance(own, Cache) and own.U.shape == (2, 3, 4, 8) and own.is_current()
+    st.length = 4
+    assert m._buffers_for_step(own, 4, like) is st
+    st.length = 5                            # a later step advanced the buffers
+    newer = ModuleCache(st, 5)
+    assert not own.is_current() and newer.is_current()
+    with pytest.raises(RuntimeError, match="advanced in place"):
+        m._buffers_for_step(own, 4, like)
+    # (3) functional semantics on request: every step gets fresh buffers, old caches stay valid
+    mf = Castle(32, heads=3, dim_head=8, inplace_cache=False)
+    st2 = mf._buffers_for_step(newer, 5, like)
+    assert st2 is not st and st2.length == 5 and torch.equal(st2.bufs[1][:, :, :5], st.bufs[1][:, :, :5])
+    # (4) a full buffer grows by copy
+    full = cache_from_buffers(*[torch.zeros(2, 3, 6, 8) for _ in range(4)], length=6)
+    st3 = m._buffers_for_step(full, 6, like)
+    assert st3 is not full._state and st3.capacity >= 7
+    # (5) explicit hand-over of caller buffers: used as they are
+    mine = [torch.zeros(2, 3, 9, 8) for _ in range(4)]
+    c = cache_from_buffers(*mine, length=3)
+    assert c.kc_cache.shape == (2, 3, 3, 8) and m._buffers_for_step(c, 3, like).bufs[2] is mine[2]
+    with pytest.raises(ValueError):
+        cache_from_buffers(*mine, length=10)
+
+
+def test_forward_chunks_bound_the_scratch():
+    from lookahead_keys_attention_b200.ops import forward_chunks
+    for B, H, per, limit in [(4, 16, 10, 1000), (4, 16, 10, 100), (8, 32, 7, 50), (1, 32, 9, 9), (3, 5, 4, 9)]:
+        seen = torch.zeros(B, H, dtype=torch.int32)
+        for b0, b1, h0, h1 in forward_chunks(B, H, per, limit):
+            assert (b1 - b0) * (h1 - h0) * per <= limit
+            assert b1 - b0 == 1 or (h0, h1) == (0, H)     # several batch rows only with all heads
+            seen[b0:b1, h0:h1] += 1
+        assert bool((seen == 1).all())
+    with pytest.raises(RuntimeError, match="more than"):
+        forward_chunks(1, 1, 11, 10)
 
 
 def test_module_signature_and_state_dict():

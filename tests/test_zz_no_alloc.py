@@ -39,6 +39,8 @@ def test_static_scratch_matches_workspace_entry_two_calls(B, H, d, t0, dtype):
     bufs_b = [b.clone() for b in base]
     ws = torch.empty(int(lib.castle_decode_workspace_bytes(ctypes.byref(prob), t0 + 1)), dtype=torch.uint8, device="cuda")
     atol = 1e-5 if dtype == torch.float32 else 2e-2
+    from oracle import castle_oracle as O
+    ocache = tuple(b[:, :, :t0].float().cpu() for b in base)   # the CPU oracle walks the same two tokens
     for step in range(2):
         news = [torch.randn(B, H, 1, d, device="cuda").to(dtype) for _ in range(6)]
         out_a = torch.empty(B, H, 1, d, device="cuda", dtype=dtype)
@@ -48,6 +50,13 @@ def test_static_scratch_matches_workspace_entry_two_calls(B, H, d, t0, dtype):
         torch.cuda.synchronize()
         check_status()
         assert torch.allclose(out_a.float(), out_b.float(), atol=atol, rtol=1e-2), f"step {step}: outputs differ"
+        # and directly against the oracle (fp32 arithmetic on the same rounded inputs)
+        ref, ocache = O.castle_decode_step(*[x.float().cpu() for x in news], ocache, d ** -0.5)
+        otol = 1e-4 if dtype == torch.float32 else 2e-2
+        err = (out_b.float().cpu() - ref).abs()
+        assert bool((err <= otol + 1e-2 * ref.abs()).all()), f"step {step}: static entry vs oracle {err.max().item():.3e}"
+        if dtype != torch.float32:   # the kernel keeps U in the cache dtype: re-round the oracle's copy as it does
+            ocache = (ocache[0].to(dtype).float(), *ocache[1:])
         n = t0 + step + 1
         for a, b, nm in zip(bufs_a, bufs_b, ("U", "qu_cache", "kc_cache", "vc_cache")):
             assert torch.allclose(a[:, :, :n].float(), b[:, :, :n].float(), atol=atol, rtol=1e-2), f"step {step}: {nm}"
