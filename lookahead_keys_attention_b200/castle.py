@@ -161,7 +161,7 @@ class Castle(nn.Module):
                 state = self._new_buffers(b, h, d, seq_len, qu.dtype, qu.device)
                 # 16-bit modules: the forward kernels write all four caches themselves (U from the final
                 # lookahead state, qu/kc/vc from the tiles they hold in shared memory)
-                fill = prefill_writes_caches(qu.dtype, d)
+                fill = prefill_writes_caches(qu.dtype, d, seq_len)
                 cache_out = tuple(state.views(seq_len)) if fill else None
                 if packed is not None:
                     out, U = castle_attention_packed(packed, self.scale, True, cache_out)

@@ -22,8 +22,8 @@ __global__ void __launch_bounds__(128) castle_selftest_kernel(int mode, const __
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const bool a_in_tmem = mode >= 9;   // 9: X (tensor memory) @ Y^T, 10: X (tensor memory) @ Y
-  const bool use_tma = mode >= 5 && !a_in_tmem;
+  const bool a_in_tmem = mode == 9 || mode == 10;   // 9: X (tensor memory) @ Y^T, 10: X (tensor memory) @ Y
+  const bool use_tma = mode >= 5 && mode <= 8;
   const int op = use_tma ? mode - 5 : mode;
 
   if (tid == 0) {

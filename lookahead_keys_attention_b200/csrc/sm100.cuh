@@ -162,6 +162,10 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int fmt, bool a_
          ((uint32_t)(M >> 4) << 24);
 }
 
+// Both operands of one product must have the same format: an instruction descriptor with fp16 in one
+// format field and bf16 in the other is rejected by the hardware (illegal instruction), so a tile the
+// threads compute is always written in the type of the inputs it is multiplied with.
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accum) {
   asm volatile(

@@ -112,10 +112,35 @@ def forward_chunks(B: int, H: int, per_pair: int, limit: int | None = None):
     return [(b, b + 1, h0, h1) for b in range(B) for h0, h1 in even(H, pairs)]
 
 
-def prefill_writes_caches(dtype: torch.dtype, d: int) -> bool:
+# From this sequence length on, bf16 callers are computed with fp16 operands.  The lookahead state W grows
+# like sqrt(N) (|W| ~ 100 at N = 8192) and the gate's and the state's 16-bit copies are what the long-range
+# gradients are made of: with 8 significant bits dqc misses |a-b| <= 2e-2 + 1e-2|b| from N ~ 8192 on, with
+# fp16's 11 bits it holds at N = 16384.  (The tensor cores cannot mix an fp16 operand with a bf16 one in a
+# single product, so the inputs are converted once instead; at these lengths that pass is < 1 % of the work.)
+# Costs: values beyond +-65504 in q/k/v saturate, and the upstream gradient is rescaled by a power of two
+# (exactly) so that small gradients do not underflow.
+LONG_SEQ_FP16 = 6144
+
+
+def compute_dtype(dtype: torch.dtype, seq_len: int) -> torch.dtype:
+    """Operand type of the kernels for a caller of `dtype`: fp16 for fp32 callers (as the reference
+    operator does, lookahead_keys_attention_triton.py:437-442) and for bf16 callers at long sequences."""
+    if dtype == torch.float16 or (dtype == torch.bfloat16 and seq_len < LONG_SEQ_FP16):
+        return dtype
+    return torch.float16
+
+
+def prefill_writes_caches(dtype: torch.dtype, d: int, seq_len: int = 0) -> bool:
     """Whether the forward kernels can fill the decode caches themselves: they store their 16-bit
     operand tiles, so the caller's dtype must be the compute dtype and dim_head a tile width."""
-    return dtype in (torch.bfloat16, torch.float16) and d in (64, 128)
+    return dtype in (torch.bfloat16, torch.float16) and compute_dtype(dtype, seq_len) == dtype and d in (64, 128)
+
+
+def _to_fp16(t: torch.Tensor) -> torch.Tensor:
+    """fp16 copy that saturates instead of overflowing to infinity."""
+    if t.dtype == torch.float16:
+        return t
+    return t.clamp(-65504.0, 65504.0).to(torch.float16)
 
 
 class _CastleAttention(torch.autograd.Function):
@@ -125,21 +150,21 @@ class _CastleAttention(torch.autograd.Function):
                                             any(ctx.needs_input_grad[:6]), cache_out)
 
     @staticmethod
-    def run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, need_grad, cache_out=None):
+    def run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, need_grad, cache_out=None, out_dtype=None):
         """Shared by the six-view and the packed operator; `need_grad` says whether to save state.
         `cache_out` = four (B, H, N, d) views of decode-cache buffers the kernels fill (prefill)."""
         _require_cuda(qc, "castle_attention")
         lib = _lib.load()
         B, H, N, d = qc.shape
-        orig_dtype = qc.dtype
-        # compute dtype: 16-bit inputs run as they are; fp32 callers run with fp16 operands
-        # (the reference operator does the same: lookahead_keys_attention_triton.py:437-442)
-        cdtype = orig_dtype if orig_dtype in (torch.bfloat16, torch.float16) else torch.float16
+        orig_dtype = qc.dtype if out_dtype is None else out_dtype
+        # compute dtype: 16-bit inputs run as they are; fp32 callers, and bf16 callers at long
+        # sequences, run with fp16 operands
+        cdtype = compute_dtype(orig_dtype, N)
         dp = 64 if d <= 64 else 128
         if d > 128 or d % 8:
             raise RuntimeError(f"castle_attention: dim_head {d} not supported (multiples of 8 up to 128)")
         if cache_out is not None:
-            if not (return_U and prefill_writes_caches(orig_dtype, d)):
+            if not (return_U and prefill_writes_caches(orig_dtype, d, N)):
                 raise RuntimeError("castle_attention: cache_out needs return_U, a 16-bit dtype and dim_head 64 or 128")
             for c in cache_out:
                 if c.shape != (B, H, N, d) or c.dtype != orig_dtype or c.stride(3) != 1:
@@ -147,7 +172,7 @@ class _CastleAttention(torch.autograd.Function):
 
         def prep(t):
             if t.dtype != cdtype:
-                t = t.to(cdtype)
+                t = _to_fp16(t)
             if dp != d:
                 t = F.pad(t, (0, dp - d))  # zero columns change no dot product; scale uses the true d
             return _aligned_view(t)
@@ -203,7 +228,16 @@ class _CastleAttention(torch.autograd.Function):
         qc, kc, vc, qu, ku, vu, out, lse, wst = ctx.saved_tensors
         B, H, N, dp = qc.shape
         d, cdtype, dev = ctx.d, ctx.cdtype, qc.device
-        do = do.to(cdtype)
+        inv_s = None
+        if do.dtype != cdtype:
+            # fp16 operands for a caller with a wider exponent range: bring the upstream gradient to a
+            # fixed magnitude with a power of two (exact; every gradient is linear in it) and undo it on
+            # the results, so that neither small gradients underflow nor large ones overflow in fp16.
+            # Everything stays on the device: no host synchronisation.
+            amax = do.detach().abs().amax().float().clamp_min(1e-30)
+            s = torch.exp2(torch.floor(torch.log2(64.0 / amax))).clamp(2.0 ** -24, 2.0 ** 24)
+            inv_s = 1.0 / s
+            do = (do.float() * s).to(cdtype)
         if dp != d:
             do = F.pad(do, (0, dp - d))
         do = _aligned_view(do)
@@ -220,13 +254,15 @@ class _CastleAttention(torch.autograd.Function):
         rc = lib.castle_bwd(ctypes.byref(prob), *[ctypes.byref(x) for x in args], lse.data_ptr(), wst.data_ptr(),
                             *[ctypes.byref(x) for x in grads], ws.data_ptr(), ws.numel(), st.data_ptr(), _stream(dev))
         _lib.check(rc, "castle_bwd")
+        def back(g):   # to the caller's dtype, undoing the power-of-two scale of the upstream gradient
+            if ctx.orig_dtype == cdtype:
+                return g
+            g = g.to(ctx.orig_dtype)
+            return g.mul_(inv_s.to(ctx.orig_dtype)) if inv_s is not None else g
+
         if packed_out:
-            g = packed[..., :d]
-            return g.to(ctx.orig_dtype) if ctx.orig_dtype != cdtype else g
-        res = [g[..., :d] for g in (gqc, gkc, gvc, gqu, gku, gvu)]
-        if ctx.orig_dtype != cdtype:
-            res = [g.to(ctx.orig_dtype) for g in res]
-        return (*res, None, None, None)
+            return back(packed[..., :d])
+        return (*[back(g[..., :d]) for g in (gqc, gkc, gvc, gqu, gku, gvu)], None, None, None)
 
 
 class _CastleAttentionPacked(torch.autograd.Function):
@@ -236,9 +272,12 @@ class _CastleAttentionPacked(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, packed, scale, return_U, cache_out=None):
+        out_dtype = packed.dtype
+        if compute_dtype(out_dtype, packed.shape[1]) != out_dtype:
+            packed = _to_fp16(packed)   # one pass over the whole projection output instead of six over its views
         qu, ku, vu, qc, kc, vc = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(6))
         return _CastleAttention.run_forward(ctx, qc, kc, vc, qu, ku, vu, scale, return_U, ctx.needs_input_grad[0],
-                                            cache_out)
+                                            cache_out, out_dtype)
 
     @staticmethod
     def backward(ctx, do, dU=None):

@@ -27,10 +27,24 @@ def _packed(B, N, H, d, seed):
     return (torch.randn(B, N, 6, H, d, device="cuda", generator=g) * PROJ_STD).bfloat16()
 
 
-@pytest.mark.parametrize("B,N,H,d,pair", [(4, 4096, 16, 64, (2, 11)), (1, 8192, 4, 128, (0, 3))])
+def _oracle_pair(ins, gout, d):
+    """fp32 oracle for one (N, d) head: the dense form while its N x N tensors are small, the blockwise
+    recurrence (same algebra, checked against the dense form on the CPU) beyond that."""
+    qu, ku, vu, qc, kc, vc = ins
+    n = qc.shape[0]
+    if n <= 4096:
+        ro, rU = O.castle_parallel(qc, kc, vc, qu, ku, vu, d ** -0.5, return_U=True)
+        return ro, rU, O.castle_parallel_bwd(qc, kc, vc, qu, ku, vu, d ** -0.5, gout)
+    ro, rU, lse = O.castle_parallel_blockwise(qc, kc, vc, qu, ku, vu, d ** -0.5, block=128)
+    return ro, rU, O.castle_parallel_bwd_blockwise(qc, kc, vc, qu, ku, vu, d ** -0.5, ro, lse, rU, gout, block=128)
+
+
+@pytest.mark.parametrize("B,N,H,d,pair", [(4, 4096, 16, 64, (2, 11)), (1, 8192, 4, 128, (0, 3)), (1, 8192, 3, 64, (0, 1)),
+                                          (1, 16384, 2, 128, (0, 1))])
 def test_sampled_pair_matches_oracle_at_full_size(B, N, H, d, pair):
-    """Config 2 (B=4 N=4096 H=16 d=64) in full, and a d=128 long-sequence case: forward, U and all six
-    gradients of one (batch, head) pair against the fp32 oracle on the same bf16 inputs."""
+    """Config 2 (B=4 N=4096 H=16 d=64) in full, and long sequences up to the long-context configuration's
+    N = 16384 at d = 128: forward, U and ALL six gradients of one (batch, head) pair inside
+    |a-b| <= 2e-2 + 1e-2|b| of the fp32 oracle on the same bf16 inputs - no weaker bar for any of them."""
     from lookahead_keys_attention_b200 import castle_attention_packed, check_status
     packed = _packed(B, N, H, d, seed=N + d).requires_grad_()
     g = torch.Generator(device="cuda").manual_seed(1)
@@ -41,27 +55,37 @@ def test_sampled_pair_matches_oracle_at_full_size(B, N, H, d, pair):
     check_status()
     b, h = pair
     ins = [packed.detach()[b, :, i, h].float().cpu() for i in range(6)]  # qu,ku,vu,qc,kc,vc  (N, d)
-    qu, ku, vu, qc, kc, vc = ins
-    ro, rU = O.castle_parallel(qc, kc, vc, qu, ku, vu, d ** -0.5, return_U=True)
-    rg = O.castle_parallel_bwd(qc, kc, vc, qu, ku, vu, d ** -0.5, gout[b, h].float().cpu())  # dqc,dkc,dvc,dqu,dku,dvu
+    ro, rU, rg = _oracle_pair(ins, gout[b, h].float().cpu(), d)          # rg: dqc,dkc,dvc,dqu,dku,dvu
     _close(out[b, h].float().cpu(), ro, "out")
     ulp = 2.0 ** -8
     _close(U[b, h].float().cpu(), rU, "U", (TOL[0] + 2 * ulp * rU.abs().max().item(), TOL[1]))
     got = packed.grad[b, :, :, h].float().cpu()  # (N, 6, d)
-    ref16 = None
+    worst = {}
     for name, slot, ref in [("dqc", 3, rg[0]), ("dkc", 4, rg[1]), ("dvc", 5, rg[2]), ("dqu", 0, rg[3]), ("dku", 1, rg[4]), ("dvu", 2, rg[5])]:
         err = (got[:, slot] - ref).abs()
-        if bool((err <= TOL[0] + TOL[1] * ref.abs()).all()):
-            continue
-        # At N = 8192 the lookahead state reaches ~100 and its 16-bit copy alone breaks the element-wise
-        # rule - for the reference's own bf16 arithmetic even more so.  Then the bar is that arithmetic:
-        # the kernel's worst error must not exceed the CPU bf16 run's.
-        if ref16 is None:
-            i16 = [packed.detach()[b, :, i, h].cpu() for i in range(6)]
-            ref16 = O.castle_parallel_bwd(i16[3], i16[4], i16[5], i16[0], i16[1], i16[2], d ** -0.5, gout[b, h].cpu())
-        k = {"dqc": 0, "dkc": 1, "dvc": 2, "dqu": 3, "dku": 4, "dvu": 5}[name]
-        e16 = (ref16[k].float() - ref).abs().max().item()
-        assert err.max().item() <= e16, f"{name}: kernel {err.max().item():.3e} vs reference-bf16 {e16:.3e}"
+        worst[name] = (round(err.max().item(), 4), round((err - TOL[0] - TOL[1] * ref.abs()).max().item(), 4))
+    print(f"N={N} d={d}: max error / worst excess over the rule per gradient: {worst}")
+    bad = {k: v for k, v in worst.items() if v[1] > 0}
+    assert not bad, f"outside |a-b| <= 2e-2 + 1e-2|b|: {bad} (all: {worst})"
+
+
+def test_upstream_gradient_rescaling_is_exact():
+    """Where bf16 callers run on fp16 operands (long sequences) the upstream gradient is rescaled by a power
+    of two: gradients of a tiny and of a large upstream gradient are the same up to that factor."""
+    from lookahead_keys_attention_b200 import castle_attention_packed, ops
+    N = ops.LONG_SEQ_FP16
+    packed = _packed(1, N, 1, 64, seed=5)
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    gout = torch.randn(1, 1, N, 64, device="cuda", generator=gen).bfloat16()
+
+    def grads(scale):
+        p = packed.clone().requires_grad_()
+        castle_attention_packed(p, 0.125, False).backward((gout.float() * scale).bfloat16())
+        return p.grad.float()
+
+    base = grads(1.0)
+    for k in (-20, 12):   # 1e-6 x and 4096 x the gradient: both out of fp16's comfortable range without the rescaling
+        assert torch.equal(grads(2.0 ** k), base * 2.0 ** k)
 
 
 def test_prefix_invariance_and_backward_linearity_config2():

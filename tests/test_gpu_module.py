@@ -205,7 +205,8 @@ def test_prefill_kernels_write_the_decode_caches(d, rotary, monkeypatch):
     assert torch.equal(cache.qu_cache, qu) and torch.equal(cache.kc_cache, kc) and torch.equal(cache.vc_cache, vc)
     ref_u = O.castle_parallel(*[t.float().cpu() for t in (qc, kc, vc, qu, ku, vu)], m.scale, return_U=True)[1]
     err = (cache.U.float().cpu() - ref_u).abs()
-    assert bool((err <= 2e-2 + 1e-2 * ref_u.abs()).all()), err.max().item()
+    # U is an un-normalised sum of up to N rows: a few bf16 ulps of its largest entry on top of the rule
+    assert bool((err <= 2e-2 + 2 * 2.0 ** -8 * ref_u.abs().max() + 1e-2 * ref_u.abs()).all()), err.max().item()
     # and the hand-off works: cached steps continue the sequence
     x2 = torch.randn(2, 3, 96, device="cuda").bfloat16()
     full = m(torch.cat((x, x2), 1))
