@@ -135,6 +135,10 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
+    override = os.environ.get("CASTLE_B200_LIB")   # a developer's own build of the same sources (other -D flags)
+    if override:
+        return _bind(ctypes.CDLL(override))
+
     def ensure():
         # compile on demand when the library is missing or was built from other sources; there is
         # no other code path to fall back to
@@ -146,7 +150,11 @@ def load():
                                    "`python -c 'import __graft_entry__ as g; g.build()'` where nvcc is "
                                    "available - this package has no fallback path") from e
     _locked(ensure)
-    lib = ctypes.CDLL(str(LIB_PATH))
+    return _bind(ctypes.CDLL(str(LIB_PATH)))
+
+
+def _bind(lib):
+    global _lib
     for name, (res, args) in _SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args

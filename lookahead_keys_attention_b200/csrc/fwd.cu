@@ -38,6 +38,7 @@ struct FwdParams {
   castle_tensor_t out;
   int32_t* status;
   int store_caches;   // also copy the Qu[K], Kc[K], Vc[K] tiles into the decode caches (prefill hand-off)
+  int split_q8;       // dim_head 64: walks of 8+ query blocks are cut after split_q8/256 of their length (0 = never)
 #ifdef CASTLE_PHASE_TIMING
   long long* timing;
 #endif
@@ -457,6 +458,18 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
   const int bh = blockIdx.x, K = blockIdx.y;
   const int b = bh / p.H, h = bh % p.H;
   const int k0 = K * kBlk;
+  // Walk segments.  With few (batch, head) pairs the grid is a single wave whose makespan is the longest
+  // walk (key block 0: every query block), so long walks are cut in two, one CTA each.  The CTA that takes
+  // the later part first rebuilds the state it would have inherited with a short pre-loop over the earlier
+  // blocks (Z, gate and W += A @ Vu only, no scores).  blockIdx.z = 0 is the LATER part: those CTAs are the heaviest, and the grid is handed
+  // out in blockIdx order, so they start first.
+  const int seg = (int)gridDim.z - 1 - (int)blockIdx.z;
+  const int walk = p.nblk - K;
+  const int cut = (p.split_q8 > 0 && walk >= 8) ? K + (walk * p.split_q8 + 128) / 256 : p.nblk;
+  const int I_begin = seg == 0 ? K : cut;              // first block whose scores this CTA computes
+  const int I_end = seg == 0 ? cut : p.nblk;           // one past its last
+  if (I_begin >= I_end) return;                        // a short walk is not cut: its later part is empty
+  const bool owns_state = (I_end == p.nblk);                                      // the last segment ends with W_K = U[K]
 
   if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
     if (tid == 0) atomicOr(p.status, CASTLE_STATUS_BAD_LAUNCH);
@@ -480,8 +493,10 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
   if (tid == 0) {
     mbar_expect_tx(bar_qu, OPB);
     tma_load_4d(sQu, &m_qu, bar_qu, 0, k0, h, b);
-    mbar_expect_tx(bar_qc, OPB);
-    tma_load_4d(sQV, &m_qc, bar_qc, 0, k0, h, b);
+    if (I_begin == K) {   // the pre-loop needs no Qc; the last pre-loop step fetches the first real one
+      mbar_expect_tx(bar_qc, OPB);
+      tma_load_4d(sQV, &m_qc, bar_qc, 0, k0, h, b);
+    }
     mbar_expect_tx(bar_ku, OPB);
     tma_load_4d(sKuA, &m_ku, bar_ku, 0, k0, h, b);
     mbar_expect_tx(bar_vu, OPB);
@@ -489,10 +504,11 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
     mbar_wait(bar_qu, 0, abortp);
     // Prefill hand-off: Qu[K] is the block's rows of the decode cache; Kc[K] and Vc[K] follow in the
     // first step, each when its fetch has landed (see there).
-    if (p.store_caches && !*abortp) tma_store_4d(&m_quc, sQu, 0, k0, h, b);
+    if (p.store_caches && seg == 0 && !*abortp) tma_store_4d(&m_quc, sQu, 0, k0, h, b);
   }
 
-  uint32_t ph_ld = 0, ph_mma = 0;   // all per-step load barriers flip once per step
+  uint32_t ph_ld = 0, ph_mma = 0;   // Ku/Vu barriers flip once per step (pre-loop steps included) ...
+  uint32_t ph_main = 0;             // ... the Qc/Kc/Vc barriers once per step that computes scores
   const uint32_t aQu = smem_u32(sQu), aQV = smem_u32(sQV), aWb = smem_u32(sWb), aKuA = smem_u32(sKuA),
                  aVuT = smem_u32(sVuT);
   const int krow = k0 + row;
@@ -507,9 +523,10 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
   tc_fence_before();   \
   __syncthreads();
 
-  for (int I = K; I < p.nblk; ++I) {
+  for (int I = K; I < I_end; ++I) {
     const int i0 = I * kBlk;
-    const bool diag = (I == K), last = (I == p.nblk - 1);
+    const bool diag = (I == K), last = (I == I_end - 1);
+    const bool pre = I < I_begin;   // state-only step of the pre-loop
 #ifdef CASTLE_PHASE_TIMING
     const int tstep = I - K;
 #endif
@@ -524,6 +541,18 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
     }
     F2_MMA_WAIT();
     PHASE_MARK(1);
+    if (pre && tid == 0) {
+      // Pre-loop steps are short, so their loads are issued as early as the slots allow: Ku[I] is consumed
+      // by Z (and the gate's shared-memory copy is not needed without scores), so the next Ku goes now,
+      // together with Qc when the next step is the first one that computes scores.
+      const int in0 = i0 + kBlk;   // a pre-loop step is never the last step of its CTA
+      if (I + 1 == I_begin) {
+        mbar_expect_tx(bar_qc, OPB);
+        tma_load_4d(sQV, &m_qc, bar_qc, 0, in0, h, b);
+      }
+      mbar_expect_tx(bar_ku, OPB);
+      tma_load_4d(sKuA, &m_ku, bar_ku, 0, in0, h, b);
+    }
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {  // gate A = sigmoid(scale * Z), kept for j > k; over Ku[I]
       const int c0 = cbase + c * 32;
@@ -536,8 +565,8 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = (c0 + j > row) ? v[j] : 0.f;
       }
-      store_row32<T>(sKuA, kPanelBytes, row, c0, v);          // operand of the Su correction (read along rows)
-      tmem_st_packed32<T>(trow + COL_O + c0 / 2, v);          // first operand of the state update
+      if (!pre) store_row32<T>(sKuA, kPanelBytes, row, c0, v);   // operand of the Su correction (read along rows)
+      tmem_st_packed32<T>(trow + COL_O + c0 / 2, v);             // first operand of the state update
     }
     tmem_st_wait();
     F2_SYNC();
@@ -546,14 +575,32 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
     // ---- W_K += A @ Vu[I]   and   T[I,I] = Qc[I] @ Vu[I]^T
     if (tid == 0) {
       mbar_wait(bar_vu, ph_ld, abortp);
-      mbar_wait(bar_qc, ph_ld, abortp);
+      if (!pre) mbar_wait(bar_qc, ph_main, abortp);
       tc_fence_after();
       gemm_tm_t<8>(tmem + COL_W, tmem + COL_O, aVuT, ID_D, !diag);
-      gemm_kk_t<1>(tmem + COL_S, aQV, aVuT, ID_SQ, false);
+      if (!pre) gemm_kk_t<1>(tmem + COL_S, aQV, aVuT, ID_SQ, false);
       mma_commit(bar_mma);
     }
     F2_MMA_WAIT();
     PHASE_MARK(3);
+    if (pre) {
+      // The state now includes block I.  Before the first step that computes scores, make its 16-bit copy
+      // (the later steps refresh it themselves); then fetch the next block's tiles and go on.
+      const bool next_real = (I + 1 == I_begin);
+      if (next_real && grp < 2) {
+        float v[32];
+        tmem_ld32(trow + COL_W + grp * 32, v);
+        tmem_ld_wait();
+        store_row32<T>(sWb, kPanelBytes, row, grp * 32, v);
+      }
+      F2_SYNC();
+      if (tid == 0) {   // Vu[I] is consumed by the state update: the next one goes now
+        mbar_expect_tx(bar_vu, OPB);
+        tma_load_4d(sVuT, &m_vu, bar_vu, 0, i0 + kBlk, h, b);
+      }
+      ph_ld ^= 1;
+      continue;
+    }
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {  // masked T (j <= i), unscaled; over Vu[I]
       const int c0 = cbase + c * 32;
@@ -604,7 +651,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
 
     // ---- S/scale = penalty + Qc[I] @ Kc[K]^T
     if (tid == 0) {
-      mbar_wait(bar_kc, ph_ld, abortp);
+      mbar_wait(bar_kc, ph_main, abortp);
       tc_fence_after();
       gemm_kk_t<1>(tmem + COL_S, aQV, aVuT, ID_SQ, true);
       mma_commit(bar_mma);
@@ -661,7 +708,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
 
     // ---- O_partial = P @ Vc[K]
     if (tid == 0) {
-      mbar_wait(bar_vc, ph_ld, abortp);
+      mbar_wait(bar_vc, ph_main, abortp);
       tc_fence_after();
       gemm_tm_t<8>(tmem + COL_O, tmem + COL_S, aQV, ID_D, false);
       mma_commit(bar_mma);
@@ -704,6 +751,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       }
     }
     ph_ld ^= 1;
+    ph_main ^= 1;
     tc_fence_before();
     __syncthreads();
     PHASE_MARK(10);
@@ -711,8 +759,8 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
 #undef F2_MMA_WAIT
 #undef F2_SYNC
 
-  // ---- W_K is now U[K]
-  if (grp < 2 && (p.u_out.ptr != nullptr || p.w_state != nullptr)) {
+  // ---- W_K is now U[K] (in the CTA that walked to the last query block)
+  if (owns_state && grp < 2 && (p.u_out.ptr != nullptr || p.w_state != nullptr)) {
     tc_fence_after();
     const int c0 = grp * 32;
     float v[32];
@@ -804,9 +852,18 @@ static int launch_fwd_d64(const FwdParams& p, const CUtensorMap* maps, cudaStrea
     cudaError_t e = cudaFuncSetAttribute(castle_fwd_kernel_d64<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwd2Smem);
     if (e != cudaSuccess) return cuda_fail(e, "castle_fwd attribute");
   }
-  dim3 grid(p.B * p.H, p.nblk);
+  // Few (batch, head) pairs: cut the long walks so that the grid is several waves of short CTAs instead of
+  // one wave bounded by the walk of key block 0 (296 CTAs are resident at a time: 2 per SM on 148 SMs).
+  FwdParams q = p;
+  q.split_q8 = 0;
+  int nseg = 1;
+  if ((int64_t)p.B * p.H * p.nblk < 384 && p.nblk >= 8) {   // beyond ~1.3 waves the pre-loops cost more than the balance gains
+    q.split_q8 = 128;   // the middle measured best (0.169 ms at 8 pairs x 32 blocks; 0.240 ms uncut; later cuts slower)
+    nseg = 2;
+  }
+  dim3 grid(p.B * p.H, p.nblk, nseg);
   ev_start(CASTLE_KERNEL_FWD, st);
-  castle_fwd_kernel_d64<T, G><<<grid, G * 128, kFwd2Smem, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+  castle_fwd_kernel_d64<T, G><<<grid, G * 128, kFwd2Smem, st>>>(q, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
                                                                  maps[6], maps[7], maps[8]);
   ev_stop(CASTLE_KERNEL_FWD, st);
   constexpr int ROWS = 256 / (64 / 8);
@@ -893,6 +950,7 @@ static int fwd_impl(const char* who, const castle_problem_t* p, const castle_ten
   fp.u_dtype = u_dtype;
   fp.out = *out; fp.status = status;
   fp.store_caches = caches ? 1 : 0;
+  fp.split_q8 = 0;
 #ifdef CASTLE_PHASE_TIMING
   fp.timing = (long long*)((char*)workspace + need);  // the caller leaves 1 KB beyond the partials
 #endif

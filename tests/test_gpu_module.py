@@ -179,14 +179,15 @@ def test_forward_chunking_of_scratch(monkeypatch):
 
 
 @torch.no_grad()
-@pytest.mark.parametrize("d,rotary", [(64, False), (128, False), (64, True)])
-def test_prefill_kernels_write_the_decode_caches(d, rotary, monkeypatch):
+@pytest.mark.parametrize("d,rotary,N", [(64, False, 333), (128, False, 333), (64, True, 333), (64, False, 1333)])
+def test_prefill_kernels_write_the_decode_caches(d, rotary, N, monkeypatch):
     """Prefill hand-off (reference: lookahead_keys_attention.py:161-164): for 16-bit modules the forward
     kernels fill all four caches themselves - U from the final lookahead state, qu/kc/vc from the tiles
     in shared memory - straight into the capacity buffers; the module makes no copy pass."""
     from lookahead_keys_attention_b200 import Castle, ModuleCache
     torch.manual_seed(7)
-    H, N = 3, 333      # 333 rows: the last key block is ragged, rows beyond N must stay untouched
+    H = 3              # N = 333: the last key block is ragged, rows beyond N must stay untouched;
+    #                    N = 1333 at dim_head 64: few pairs and 11 key blocks, so the walks run as segments
     m = Castle(96, heads=H, dim_head=d, rotary_emb=rotary).cuda().bfloat16()
     x = torch.randn(2, N, 96, device="cuda").bfloat16()
     copies = []

@@ -54,6 +54,30 @@ def test_forward_matches_oracle(B, H, N, d, dtype):
     assert torch.equal(out2, out)
 
 
+@pytest.mark.parametrize("B,H,N", [(1, 2, 1100), (2, 1, 2048), (1, 1, 3000)])
+def test_forward_walk_segments_match_oracle(B, H, N):
+    """Few (batch, head) pairs and many key blocks: the dim_head-64 forward cuts each long walk into
+    segments, and a segment that starts mid-walk rebuilds its lookahead state with a state-only pre-loop.
+    Output, U (written by the last segment only) and the saved state (through the backward) must match."""
+    from lookahead_keys_attention_b200 import castle_attention, check_status
+    d, scale = 64, 0.125
+    packed = (_inputs(B, H, N, d, torch.float32, seed=N) * 3 ** -0.5).bfloat16()
+    views = [t.cuda().requires_grad_() for t in _views(packed)]
+    qu, ku, vu, qc, kc, vc = views
+    out, U = castle_attention(qc, kc, vc, qu, ku, vu, scale, True)
+    gout = torch.randn(B, H, N, d, generator=torch.Generator().manual_seed(1)).bfloat16()
+    out.backward(gout.cuda())
+    torch.cuda.synchronize()
+    check_status()
+    r = [t.float() for t in _views(packed)]
+    ro, rU = O.castle_parallel(r[3], r[4], r[5], r[0], r[1], r[2], scale, return_U=True)
+    _close(out.float().cpu(), ro, *BF16_TOL, "out")
+    _close(U.float().cpu(), rU, BF16_TOL[0] + 2 * 2.0 ** -8 * rU.abs().max().item(), BF16_TOL[1], "U")
+    rg = O.castle_parallel_bwd(r[3], r[4], r[5], r[0], r[1], r[2], scale, gout.float())   # dqc,dkc,dvc,dqu,dku,dvu
+    for name, t, ref in zip(("dqc", "dkc", "dvc", "dqu", "dku", "dvu"), (qc, kc, vc, qu, ku, vu), rg):
+        _close(t.grad.float().cpu(), ref, *BF16_TOL, name)
+
+
 @pytest.mark.parametrize("name", ["core_n40_d16", "core_n200_d64", "core_n130_d128"])
 def test_forward_matches_reference_golden(name):
     from lookahead_keys_attention_b200 import castle_attention
