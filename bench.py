@@ -237,16 +237,35 @@ def run_ours(args):
     fwd_tflops = rank_f_fwd / (fwd_ms * 1e-3) / 1e12
 
     # ---- end-to-end arm: the module called with host tensors
-    out_host = torch.empty(bs, N, dim, dtype=torch.bfloat16).pin_memory()
-    dx_host = torch.empty(bs, N, dim, dtype=torch.bfloat16).pin_memory()
     group = None
-    if world > B and not weak:  # ranks that share a batch row hold different heads: their projections' outputs add up
+    run_layer = layer
+    if world > B and not weak:
+        # Ranks that share a batch row split its heads for the attention core.  The projections around the
+        # core are split by POSITIONS instead (full weights on every rank) and the tensors change hands by an
+        # all-to-all inside the row's group before and after the core, so every rank uploads, projects and
+        # downloads only its own positions and nothing is summed across ranks.
         import torch.distributed as dist
+        from lookahead_keys_attention_b200.sharding import Shard, heads_to_rows, rows_to_heads
         per = world // B
         for b in range(B):
             grp = dist.new_group(list(range(b * per, (b + 1) * per)))
             if b == shard.b0:
                 group = grp
+        full = make_layer(Shard(shard.b0, shard.b1, 0, H), dev)
+        n_r = N // per
+        r0 = (rank % per) * n_r
+        x_host = x_host[:, r0:r0 + n_r].contiguous().pin_memory()
+        g_host = g_host[:, r0:r0 + n_r].contiguous().pin_memory()
+
+        def run_layer(x):
+            qkv = full.to_all_qkv(full.norm(x))
+            packed_h = rows_to_heads(qkv.view(1, n_r, 6, H, d), group)            # every position, this rank's heads
+            o = castle_attention_packed(packed_h, scale, False)                     # (1, H/per, N, d)
+            return full.combine_heads(heads_to_rows(o, group))                     # this rank's positions
+
+        layer = full   # its parameters are the ones whose gradients are cleared per step
+    out_host = torch.empty_like(x_host).pin_memory()
+    dx_host = torch.empty_like(x_host).pin_memory()
 
     # Host copies run on their own streams, double-buffered: the H2D copy of step s+1 and the D2H
     # copy of step s-1 overlap the compute of step s.  Every step still copies its own inputs in
@@ -282,13 +301,9 @@ def run_ours(args):
             x = dbuf[slot][0].detach().requires_grad_()
             for p_ in layer.parameters():
                 p_.grad = None
-            out = layer(x)
+            out = run_layer(x)
             out.backward(dbuf[slot][1])
             dx, o = x.grad, out.detach()
-            if group is not None:
-                import torch.distributed as dist
-                dist.all_reduce(o, group=group)
-                dist.all_reduce(dx, group=group)
             hold[slot] = (o, dx)
             ev_free[slot].record(main)
             ev_done.record(main)
@@ -321,7 +336,9 @@ def run_ours(args):
                    "l2": "inputs_exceed_l2 (q/k/v, grads and scratch of one step are > 126 MB)"},
         "frac_of_tensor_peak": round(value / (peaks["tflops"] * world), 4),
         "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(ms_e2e, 4),
-                "h2d_bytes_per_step": 2 * x_host.numel() * 2 * world, "d2h_bytes_per_step": 2 * out_host.numel() * 2 * world},
+                "h2d_bytes_per_step": 2 * x_host.numel() * 2 * world,
+                "d2h_bytes_per_step": 2 * out_host.numel() * 2 * world,
+                "exchange": None if group is None else "positions <-> heads all-to-all inside each batch row's group, twice per pass"},
         "gpu_launches": 5 * args.steps,
         "kernels": {"fwd_main_ms": round(fwd_ms, 4), "fwd_main_tflops": round(fwd_tflops, 2),
                     "bwd_main_ms": round(bwd_ms, 4), "bwd_main_tflops": round(bwd_tflops, 2)},
