@@ -96,6 +96,18 @@ int castle_fwd_prefill(const castle_problem_t* p, const castle_tensor_t* qc, con
                        const castle_tensor_t* kc_cache, const castle_tensor_t* vc_cache, float* w_state,
                        void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* ---- 16-bit element-type conversion -----------------------------------------
+ * Replaces the `.half()` casts of CastleAttentionFunction
+ * (lookahead_keys_attention_triton.py:437-442, :523) for bf16 callers that are
+ * computed with fp16 operands: one pass over `count` contiguous elements
+ * (a multiple of 8; pointers 16-byte aligned).  src_dtype CASTLE_BF16: bf16 ->
+ * fp16, saturating at +-65504; CASTLE_F16: fp16 -> bf16.  `mul` (device
+ * pointer to one float, may be NULL) multiplies every element on the way, which
+ * is how the upstream gradient is rescaled by a power of two and the gradients
+ * scaled back without a host synchronisation.
+ */
+int castle_convert_16bit(int32_t src_dtype, const void* src, void* dst, int64_t count, const float* mul, void* stream);
+
 /* ---- parallel backward ---------------------------------------------------
  * Replaces CastleAttentionFunction.backward
  * (lookahead_keys_attention_triton.py:509-602) with its two kernels

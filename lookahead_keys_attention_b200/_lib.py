@@ -14,7 +14,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libcastle_b200.so"
-SOURCES = ["api.cu", "decode.cu", "selftest.cu", "fwd.cu", "bwd.cu", "bwd128.cu"]
+SOURCES = ["api.cu", "decode.cu", "selftest.cu", "convert.cu", "fwd.cu", "bwd.cu", "bwd128.cu"]
 
 BF16, F16, F32 = 0, 1, 2
 
@@ -118,6 +118,7 @@ _SIGNATURES = {
     "castle_fwd_workspace_bytes": (_sz, [_PR]),
     "castle_fwd": (ctypes.c_int, [_PR] + [_T] * 7 + [_vp, _T, _i32, _vp, _vp, _sz, _vp, _vp]),
     "castle_fwd_prefill": (ctypes.c_int, [_PR] + [_T] * 7 + [_vp] + [_T] * 4 + [_vp, _vp, _sz, _vp, _vp]),
+    "castle_convert_16bit": (ctypes.c_int, [_i32, _vp, _vp, ctypes.c_int64, _vp, _vp]),
     "castle_bwd_workspace_bytes": (_sz, [_PR]),
     "castle_bwd": (ctypes.c_int, [_PR] + [_T] * 8 + [_vp, _vp] + [_T] * 6 + [_vp, _sz, _vp, _vp]),
     "castle_decode_workspace_bytes": (_sz, [_PR, _i32]),

@@ -276,12 +276,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// sigmoid at the precision of the operand type: one MUFU op (tanh) when the result is rounded
-// to bf16 anyway, exp + divide when it feeds fp16 operands (which carry three more mantissa bits)
+// sigmoid as one special-function op: 0.5 * tanh.approx(x / 2) + 0.5.  tanh.approx is good to about 2^-11,
+// i.e. the result to ~2.4e-4: below bf16 rounding (2e-3) and at the level of fp16 rounding (2.4e-4) of the
+// operand tiles the result is packed into.  (An exp-and-divide form costs two special-function ops.)
 template <typename T>
 __device__ __forceinline__ float sigmoid_t(float x) {
-  if constexpr (Elem<T>::fmt == 1) return fmaf(0.5f, tanh_approx(0.5f * x), 0.5f);
-  else return __fdividef(1.f, 1.f + __expf(-x));
+  return fmaf(0.5f, tanh_approx(0.5f * x), 0.5f);
 }
 
 // Write 32 consecutive elements (columns c0..c0+31, c0 a multiple of 32) of row `row`

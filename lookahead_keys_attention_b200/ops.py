@@ -90,7 +90,7 @@ def _stream(device):
 # Bound on the forward's scratch per launch.  The soft-max partials take N^2/128 * (8 + 2*d) bytes
 # per (batch, head) pair (O(N^2), where the reference kernel needs O(N*d)), so a call is cut into
 # launches over whole batch rows, or over head ranges of one batch row, that each stay below it.
-MAX_WORKSPACE_BYTES = 8 << 30
+MAX_WORKSPACE_BYTES = 16 << 30
 
 
 def forward_chunks(B: int, H: int, per_pair: int, limit: int | None = None):
@@ -136,10 +136,22 @@ def prefill_writes_caches(dtype: torch.dtype, d: int, seq_len: int = 0) -> bool:
     return dtype in (torch.bfloat16, torch.float16) and compute_dtype(dtype, seq_len) == dtype and d in (64, 128)
 
 
+def _convert_16bit(t: torch.Tensor, mul: torch.Tensor | None = None) -> torch.Tensor:
+    """One pass: contiguous bf16 -> fp16 (saturating) or fp16 -> bf16, times the device scalar `mul`."""
+    lib = _lib.load()
+    out = torch.empty_like(t, dtype=torch.float16 if t.dtype == torch.bfloat16 else torch.bfloat16)
+    rc = lib.castle_convert_16bit(_DTYPES[t.dtype], t.data_ptr(), out.data_ptr(), t.numel(),
+                                  mul.data_ptr() if mul is not None else None, _stream(t.device))
+    _lib.check(rc, "castle_convert_16bit")
+    return out
+
+
 def _to_fp16(t: torch.Tensor) -> torch.Tensor:
     """fp16 copy that saturates instead of overflowing to infinity."""
     if t.dtype == torch.float16:
         return t
+    if t.dtype == torch.bfloat16 and t.is_cuda and t.is_contiguous() and t.numel() % 8 == 0 and t.data_ptr() % 16 == 0:
+        return _convert_16bit(t)
     return t.clamp(-65504.0, 65504.0).to(torch.float16)
 
 
@@ -236,8 +248,11 @@ class _CastleAttention(torch.autograd.Function):
             # Everything stays on the device: no host synchronisation.
             amax = do.detach().abs().amax().float().clamp_min(1e-30)
             s = torch.exp2(torch.floor(torch.log2(64.0 / amax))).clamp(2.0 ** -24, 2.0 ** 24)
-            inv_s = 1.0 / s
-            do = (do.float() * s).to(cdtype)
+            inv_s = (1.0 / s).reshape(1)
+            if do.dtype == torch.bfloat16 and do.is_contiguous() and do.numel() % 8 == 0 and do.data_ptr() % 16 == 0:
+                do = _convert_16bit(do, s.reshape(1))
+            else:
+                do = (do.float() * s).to(cdtype)
         if dp != d:
             do = F.pad(do, (0, dp - d))
         do = _aligned_view(do)
@@ -257,6 +272,8 @@ class _CastleAttention(torch.autograd.Function):
         def back(g):   # to the caller's dtype, undoing the power-of-two scale of the upstream gradient
             if ctx.orig_dtype == cdtype:
                 return g
+            if ctx.orig_dtype == torch.bfloat16 and g.is_contiguous() and g.numel() % 8 == 0:
+                return _convert_16bit(g, inv_s)
             g = g.to(ctx.orig_dtype)
             return g.mul_(inv_s.to(ctx.orig_dtype)) if inv_s is not None else g
 
