@@ -418,13 +418,19 @@ constexpr uint32_t kFwd2Smem = 7 * kPanelBytes + 256;   // 112 KB of tiles + bar
 #endif
 constexpr int kFwd2Groups = CASTLE_FWD_GROUPS;
 
-template <typename T, int G>
+// Tensor maps of the three decode caches a prefill launch stores into; the plain launch carries an empty
+// struct instead.  AUX = the kernel with the two rarely needed paths (cache stores, cut walks) compiled in:
+// as run-time branches of the one kernel they cost the plain path 2.3 % (1.001 against 0.979 ms on the bench
+// workload), so the plain instantiation has none of their code or parameters.
+template <bool AUX> struct CacheMaps {};
+template <> struct CacheMaps<true> { CUtensorMap qu, kc, vc; };
+
+template <typename T, int G, bool AUX>
 __global__ void __launch_bounds__(G * 128, 2)
 castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_qc, const __grid_constant__ CUtensorMap m_kc,
                       const __grid_constant__ CUtensorMap m_vc, const __grid_constant__ CUtensorMap m_qu,
                       const __grid_constant__ CUtensorMap m_ku, const __grid_constant__ CUtensorMap m_vu,
-                      const __grid_constant__ CUtensorMap m_quc, const __grid_constant__ CUtensorMap m_kcc,
-                      const __grid_constant__ CUtensorMap m_vcc) {
+                      const __grid_constant__ CacheMaps<AUX> m_cache) {
   constexpr int D = 64;
   constexpr int NCH = 4 / G;   // 32-column chunks of a 128-column tile per thread
   constexpr uint32_t OPB = kPanelBytes;
@@ -463,9 +469,12 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
   // the later part first rebuilds the state it would have inherited with a short pre-loop over the earlier
   // blocks (Z, gate and W += A @ Vu only, no scores).  blockIdx.z = 0 is the LATER part: those CTAs are the heaviest, and the grid is handed
   // out in blockIdx order, so they start first.
-  const int seg = (int)gridDim.z - 1 - (int)blockIdx.z;
+  const int seg = AUX ? (int)gridDim.z - 1 - (int)blockIdx.z : 0;
   const int walk = p.nblk - K;
-  const int cut = (p.split_q8 > 0 && walk >= 8) ? K + (walk * p.split_q8 + 128) / 256 : p.nblk;
+  const int cut = (AUX && p.split_q8 > 0 && walk >= 8) ? K + (walk * p.split_q8 + 128) / 256 : p.nblk;
+  const bool store_caches = AUX && p.store_caches;
+  const CUtensorMap *m_cache_qu = nullptr, *m_cache_kc = nullptr, *m_cache_vc = nullptr;
+  if constexpr (AUX) { m_cache_qu = &m_cache.qu; m_cache_kc = &m_cache.kc; m_cache_vc = &m_cache.vc; }
   const int I_begin = seg == 0 ? K : cut;              // first block whose scores this CTA computes
   const int I_end = seg == 0 ? cut : p.nblk;           // one past its last
   if (I_begin >= I_end) return;                        // a short walk is not cut: its later part is empty
@@ -504,7 +513,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
     mbar_wait(bar_qu, 0, abortp);
     // Prefill hand-off: Qu[K] is the block's rows of the decode cache; Kc[K] and Vc[K] follow in the
     // first step, each when its fetch has landed (see there).
-    if (p.store_caches && seg == 0 && !*abortp) tma_store_4d(&m_quc, sQu, 0, k0, h, b);
+    if (store_caches && seg == 0 && !*abortp) tma_store_4d(m_cache_qu, sQu, 0, k0, h, b);
   }
 
   uint32_t ph_ld = 0, ph_mma = 0;   // Ku/Vu barriers flip once per step (pre-loop steps included) ...
@@ -526,7 +535,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
   for (int I = K; I < I_end; ++I) {
     const int i0 = I * kBlk;
     const bool diag = (I == K), last = (I == I_end - 1);
-    const bool pre = I < I_begin;   // state-only step of the pre-loop
+    const bool pre = AUX && I < I_begin;   // state-only step of the pre-loop
 #ifdef CASTLE_PHASE_TIMING
     const int tstep = I - K;
 #endif
@@ -655,7 +664,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       tc_fence_after();
       gemm_kk_t<1>(tmem + COL_S, aQV, aVuT, ID_SQ, true);
       mma_commit(bar_mma);
-      if (diag && p.store_caches && !*abortp) tma_store_4d(&m_kcc, sVuT, 0, k0, h, b);
+      if (diag && store_caches && !*abortp) tma_store_4d(m_cache_kc, sVuT, 0, k0, h, b);
     }
     F2_MMA_WAIT();
     PHASE_MARK(7);
@@ -712,8 +721,8 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       tc_fence_after();
       gemm_tm_t<8>(tmem + COL_O, tmem + COL_S, aQV, ID_D, false);
       mma_commit(bar_mma);
-      if (diag && p.store_caches) {
-        if (!*abortp) tma_store_4d(&m_vcc, sQV, 0, k0, h, b);
+      if (diag && store_caches) {
+        if (!*abortp) tma_store_4d(m_cache_vc, sQV, 0, k0, h, b);
         bulk_commit();
       }
     }
@@ -730,7 +739,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
     PHASE_MARK(9);
     if (tid == 0 && !last) {  // every slot of this step is dead: fetch the next step's Qc, Ku, Vu
       const int in0 = i0 + kBlk;
-      if (diag && p.store_caches) bulk_wait_read0();   // the cache stores have read the Kc and Vc slots
+      if (diag && store_caches) bulk_wait_read0();   // the cache stores have read the Kc and Vc slots
       mbar_expect_tx(bar_qc, OPB);
       tma_load_4d(sQV, &m_qc, bar_qc, 0, in0, h, b);
       mbar_expect_tx(bar_ku, OPB);
@@ -800,7 +809,7 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
       }
     }
   }
-  if (p.store_caches && tid == 0) bulk_wait0();
+  if (store_caches && tid == 0) bulk_wait0();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, TM_COLS);
@@ -849,22 +858,28 @@ template <typename T>
 static int launch_fwd_d64(const FwdParams& p, const CUtensorMap* maps, cudaStream_t st) {
   constexpr int G = kFwd2Groups;
   {  // per device, so set on every call (cheap)
-    cudaError_t e = cudaFuncSetAttribute(castle_fwd_kernel_d64<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwd2Smem);
+    cudaError_t e = cudaFuncSetAttribute(castle_fwd_kernel_d64<T, G, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwd2Smem);
     if (e != cudaSuccess) return cuda_fail(e, "castle_fwd attribute");
   }
   // Few (batch, head) pairs: cut the long walks so that the grid is several waves of short CTAs instead of
   // one wave bounded by the walk of key block 0 (296 CTAs are resident at a time: 2 per SM on 148 SMs).
   FwdParams q = p;
   q.split_q8 = 0;
-  int nseg = 1;
-  if ((int64_t)p.B * p.H * p.nblk < 384 && p.nblk >= 8) {   // beyond ~1.3 waves the pre-loops cost more than the balance gains
+  if ((int64_t)p.B * p.H * p.nblk < 384 && p.nblk >= 8)   // beyond ~1.3 waves the pre-loops cost more than the balance gains
     q.split_q8 = 128;   // the middle measured best (0.169 ms at 8 pairs x 32 blocks; 0.240 ms uncut; later cuts slower)
-    nseg = 2;
-  }
-  dim3 grid(p.B * p.H, p.nblk, nseg);
+  const bool aux = q.split_q8 > 0 || p.store_caches;
+  dim3 grid(p.B * p.H, p.nblk, q.split_q8 > 0 ? 2 : 1);
   ev_start(CASTLE_KERNEL_FWD, st);
-  castle_fwd_kernel_d64<T, G><<<grid, G * 128, kFwd2Smem, st>>>(q, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
-                                                                 maps[6], maps[7], maps[8]);
+  if (aux) {
+    cudaError_t e = cudaFuncSetAttribute(castle_fwd_kernel_d64<T, G, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFwd2Smem);
+    if (e != cudaSuccess) return cuda_fail(e, "castle_fwd attribute");
+    CacheMaps<true> cm;
+    cm.qu = maps[6]; cm.kc = maps[7]; cm.vc = maps[8];
+    castle_fwd_kernel_d64<T, G, true><<<grid, G * 128, kFwd2Smem, st>>>(q, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], cm);
+  } else {
+    castle_fwd_kernel_d64<T, G, false><<<grid, G * 128, kFwd2Smem, st>>>(q, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5],
+                                                                        CacheMaps<false>{});
+  }
   ev_stop(CASTLE_KERNEL_FWD, st);
   constexpr int ROWS = 256 / (64 / 8);
   dim3 g2(p.nblk * (kBlk / ROWS), p.B * p.H);
