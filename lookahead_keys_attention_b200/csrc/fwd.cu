@@ -523,8 +523,8 @@ castle_fwd_kernel_d64(const FwdParams p, const __grid_constant__ CUtensorMap m_q
   const int krow = k0 + row;
   const float sl2 = p.scale * kLog2e;
 
-#define F2_MMA_WAIT()                   \
-  mbar_wait(bar_mma, ph_mma, abortp);   \
+#define F2_MMA_WAIT()                              \
+  mbar_wait_lazy_abort(bar_mma, ph_mma, abortp);   \
   ph_mma ^= 1;                          \
   tc_fence_after();
 #define F2_SYNC()      \
