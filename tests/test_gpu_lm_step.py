@@ -79,6 +79,33 @@ def test_lm_step_matches_oracle_stack():
         assert rel < 5e-2, f"{n}: rel-F {rel:.3e}"
 
 
+def test_lm_step_full_depth_matches_oracle_stack():
+    """The benchmark model at its full depth and width (8 layers, dim 512, 8 heads x 64, 1024 tokens) on a
+    quarter of its batch: loss and gradient norm of one bf16 step against the same stack with the attention
+    core evaluated by the CPU oracle in fp32 on the same bf16-rounded weights."""
+    from lookahead_keys_attention_b200 import Castle, check_status
+    torch.manual_seed(3)
+    ours = ByteLM(8, 512, 8, 64, Castle).cuda().bfloat16()
+    ref = ByteLM(8, 512, 8, 64, OracleCastle)
+    ref.load_state_dict({k: v.float().cpu() for k, v in ours.state_dict().items()})
+    ids = torch.randint(0, 256, (4, 1025))
+    loss = ours(ids.cuda())
+    loss.backward()
+    check_status()
+    loss_ref = ref(ids)
+    loss_ref.backward()
+    assert abs(loss.item() - loss_ref.item()) < 3e-2, (loss.item(), loss_ref.item())
+    gn = torch.sqrt(sum((p.grad.float() ** 2).sum() for p in ours.parameters())).item()
+    gn_ref = torch.sqrt(sum((p.grad ** 2).sum() for p in ref.parameters())).item()
+    assert abs(gn - gn_ref) <= 5e-2 * gn_ref, (gn, gn_ref)
+    # the attention projections of the first and the last layer, where errors of the whole stack show
+    for name in ("attn.0.to_all_qkv.weight", "attn.7.to_all_qkv.weight", "attn.7.combine_heads.weight"):
+        a = dict(ours.named_parameters())[name].grad.float().cpu()
+        b = dict(ref.named_parameters())[name].grad
+        rel = ((a - b).norm() / (b.norm() + 1e-6)).item()
+        assert rel < 8e-2, f"{name}: rel-F {rel:.3e}"
+
+
 def test_lm_training_steps_full_size():
     from lookahead_keys_attention_b200 import Castle, check_status
     torch.manual_seed(0)
