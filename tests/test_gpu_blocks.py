@@ -60,3 +60,22 @@ def test_mma_rate_rejects_bad_arguments():
     assert lib.castle_selftest_mma_rate(0, 96, 8, cyc.data_ptr(), st.data_ptr(), None) < 0
     assert lib.castle_selftest_mma_rate(0, 128, 0, cyc.data_ptr(), st.data_ptr(), None) < 0
     assert lib.castle_selftest_mma_rate(0, 128, 8, None, st.data_ptr(), None) < 0
+
+
+def test_convert_16bit_saturates_and_scales():
+    """bf16 -> fp16 saturates at the fp16 range instead of overflowing; both directions apply the device-resident factor."""
+    from lookahead_keys_attention_b200 import _lib
+    lib = _lib.load()
+    x = torch.tensor([1.0, -2.5, 7e4, -3e38, 6e-5, 0.0, 123.0, -0.375] * 4, device="cuda").bfloat16()
+    y = torch.empty_like(x, dtype=torch.float16)
+    _lib.check(lib.castle_convert_16bit(_lib.BF16, x.data_ptr(), y.data_ptr(), x.numel(), None, None), "convert")
+    assert torch.equal(y.float(), x.float().clamp(-65504.0, 65504.0).half().float())
+    mul = torch.tensor([0.25], device="cuda")
+    _lib.check(lib.castle_convert_16bit(_lib.BF16, x.data_ptr(), y.data_ptr(), x.numel(), mul.data_ptr(), None), "convert")
+    assert torch.equal(y.float(), (x.float() * 0.25).clamp(-65504.0, 65504.0).half().float())
+    h = torch.randn(64, device="cuda").half()
+    b = torch.empty_like(h, dtype=torch.bfloat16)
+    mul.fill_(8.0)
+    _lib.check(lib.castle_convert_16bit(_lib.F16, h.data_ptr(), b.data_ptr(), h.numel(), mul.data_ptr(), None), "convert")
+    torch.cuda.synchronize()
+    assert torch.equal(b.float(), (h.float() * 8.0).bfloat16().float())

@@ -53,6 +53,22 @@ def test_argument_rejection_without_gpu():
     assert lib.castle_bwd_workspace_bytes(ctypes.byref(prob)) == 128 * (3 * 64 + 1) * 4
 
 
+def test_new_entry_points_reject_bad_arguments_without_gpu():
+    L = _lib()
+    lib = L.load()
+    prob = L.CastleProblem(1, 1, 128, 64, L.BF16, 0.125)
+    t = L.CastleTensor(16, 0, 0, 64)
+    r = ctypes.byref(t)
+    # prefill: the four caches are mandatory
+    rc = lib.castle_fwd_prefill(ctypes.byref(prob), *([r] * 7), None, None, r, r, r, None, None, 0, None, None)
+    assert rc < 0 and "cache" in L.last_error()
+    # conversion: only 16-bit sources, counts in multiples of 8, aligned pointers
+    assert lib.castle_convert_16bit(L.F32, 16, 32, 64, None, None) < 0 and "bf16 or fp16" in L.last_error()
+    assert lib.castle_convert_16bit(L.BF16, 16, 32, 12, None, None) < 0 and "multiple of 8" in L.last_error()
+    assert lib.castle_convert_16bit(L.BF16, 8, 32, 64, None, None) < 0
+    assert lib.castle_convert_16bit(L.BF16, None, 32, 64, None, None) < 0
+
+
 def test_ops_refuse_cpu_tensors():
     from lookahead_keys_attention_b200 import castle_attention
     z = torch.zeros(1, 1, 8, 64)
