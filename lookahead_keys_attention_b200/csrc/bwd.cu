@@ -529,8 +529,8 @@ using namespace castle;
 extern "C" size_t castle_bwd_workspace_bytes(const castle_problem_t* p) {
   if (!p || p->seq_len <= 0) return 0;
   int64_t rows = (int64_t)p->batch * p->heads * p->seq_len;
-  int nacc = p->dim_head == 128 ? 4 : 3;
-  return (size_t)(rows * (nacc * p->dim_head + 1) * sizeof(float));
+  size_t tiles = p->dim_head == 128 ? bwd128_tile_bytes(p->batch * p->heads, (p->seq_len + kBlkB - 1) / kBlkB) : 0;
+  return tiles + (size_t)(rows * (3 * p->dim_head + 1) * sizeof(float));
 }
 
 extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
@@ -561,11 +561,14 @@ extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, 
   bp.B = p->batch; bp.H = p->heads; bp.N = p->seq_len; bp.nblk = nblk; bp.scale = p->scale;
   bp.lse = lse; bp.w_state = w_state;
   int64_t rows = (int64_t)p->batch * p->heads * p->seq_len;
-  bp.acc_dqc = (float*)workspace;
+  // dim_head 128: the tile hand-over scratch comes first (a multiple of 32 KB, so what follows stays aligned)
+  const size_t tile_bytes = p->dim_head == 128 ? bwd128_tile_bytes(p->batch * p->heads, nblk) : 0;
+  bp.tiles = (uint8_t*)workspace;
+  bp.ntiles = 0; bp.bh0 = 0;
+  bp.acc_dqc = (float*)((uint8_t*)workspace + tile_bytes);
   bp.acc_dvu = bp.acc_dqc + rows * p->dim_head;
   bp.acc_dku = bp.acc_dvu + rows * p->dim_head;
-  bp.acc_dqu = bp.acc_dku + rows * p->dim_head;                       // dim_head 128 only
-  bp.delta = (p->dim_head == 128 ? bp.acc_dqu : bp.acc_dku) + rows * p->dim_head;
+  bp.delta = bp.acc_dku + rows * p->dim_head;
   bp.out = *out; bp.dout = *dout;
   bp.dqc = *dqc; bp.dkc = *dkc; bp.dvc = *dvc; bp.dqu = *dqu; bp.dku = *dku; bp.dvu = *dvu;
   bp.status = status;

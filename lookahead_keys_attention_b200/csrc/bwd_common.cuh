@@ -18,7 +18,10 @@ struct BwdParams {
   float* acc_dqc;        // [BH][N][D] fp32, zeroed
   float* acc_dvu;
   float* acc_dku;
-  float* acc_dqu;        // used at dim_head 128 only (there dqu is reduced per step as well)
+  uint8_t* tiles;        // dim_head 128: per (pair, query block, key block) the 32 KB tiles A | dSu | Tm that the
+                         // key/value kernel hands to the lookahead kernel
+  int64_t ntiles;        // query-block x key-block pairs per (batch, head) pair
+  int bh0;               // dim_head 128: first (batch, head) pair of this launch (the pairs run in chunks)
   castle_tensor_t out, dout;
   castle_tensor_t dqc, dkc, dvc, dqu, dku, dvu;
   int32_t* status;
@@ -53,7 +56,7 @@ __global__ void castle_bwd_delta_kernel(const BwdParams p) {
 }
 
 // fp32 accumulators -> scaled 16-bit gradients in the caller's (strided) tensors.
-// NACC = 3: dqc, dvu, dku;  NACC = 4: also dqu.
+// NACC = 3: dqc, dvu, dku (dqu is written by the kernel that owns the key block).
 template <typename T, int D, int NACC>
 __global__ void castle_bwd_finish_kernel(const BwdParams p) {
   constexpr int LPR = D / 8;
@@ -61,8 +64,8 @@ __global__ void castle_bwd_finish_kernel(const BwdParams p) {
   const int sub = threadIdx.x % LPR;
   if (row >= (int64_t)p.B * p.H * p.N) return;
   int bh = row / p.N, i = row % p.N, b = bh / p.H, h = bh % p.H;
-  const float* srcs[4] = {p.acc_dqc, p.acc_dvu, p.acc_dku, p.acc_dqu};
-  const castle_tensor_t* dsts[4] = {&p.dqc, &p.dvu, &p.dku, &p.dqu};
+  const float* srcs[3] = {p.acc_dqc, p.acc_dvu, p.acc_dku};
+  const castle_tensor_t* dsts[3] = {&p.dqc, &p.dvu, &p.dku};
 #pragma unroll
   for (int t = 0; t < NACC; ++t) {
     const float4* s4 = reinterpret_cast<const float4*>(srcs[t] + row * D + sub * 8);
@@ -76,6 +79,7 @@ __global__ void castle_bwd_finish_kernel(const BwdParams p) {
 }
 
 // dim_head 128 backward (bwd128.cu)
+size_t bwd128_tile_bytes(int BH, int nblk);   // scratch of the tile hand-over between its two kernels
 int launch_bwd128(const BwdParams& p, int dtype, const CUtensorMap* in_maps, cudaStream_t st);
 
 }  // namespace castle
