@@ -2,14 +2,20 @@
 //
 // At d = 128 the five per-key-block accumulators of the d = 64 kernel (W, G, dkc, dvc, dqu) would
 // need 640 TMEM columns, and seven 32 KB operand tiles already fill shared memory.  The pass is
-// therefore split into two kernels, each walking the query blocks I downwards for one key block
-// K and recomputing the scores (Z, gate, peeled state W, T, Su, Sc) the way the d = 64 kernel does:
+// therefore split into two kernels, each walking the query blocks I downwards for one key block K:
 //
-//   castle_bwd128_kv_kernel   TMEM: W | dkc | dvc | scratch.  Accumulates dkc, dvc in TMEM; builds
-//                             dqc[I] = dS@Kc + dSu@Wb + dT@Vu in the scratch and adds it to the
-//                             fp32 workspace with a TMA reduce.
-//   castle_bwd128_la_kernel   TMEM: W | G | scratch | scratch.  Carries the reverse state G and
-//                             reduces dvu[I], dku[I] and dqu[K] per step.
+//   castle_bwd128_kv_kernel   TMEM: W | dkc | dvc | scratch.  Recomputes the scores (Z, gate, peeled
+//                             state W, T, Su, Sc) the way the d = 64 kernel does, accumulates dkc and
+//                             dvc in TMEM, builds dqc[I] = dS@Kc + dSu@Wb + dT@Vu in the scratch and
+//                             adds it to the fp32 workspace with a TMA reduce.  It also stores the gate A,
+//                             dSu and the masked T of every (I, K) step to a global scratch, as the
+//                             16-bit tiles lie in shared memory (3 x 32 KB per step).
+//   castle_bwd128_la_kernel   TMEM: dqu | G | scratch | scratch.  Runs after it on the same stream,
+//                             loads those three tiles and recomputes nothing: carries the reverse
+//                             state G and dqu[K] in TMEM and reduces dvu[I], dku[I] per step.
+//
+// The scratch is bounded (see kTileScratchLimit): the (batch, head) pairs run in chunks, one launch
+// of each kernel per chunk.
 //
 // Shared memory is seven 32 KB slots that are re-used as tiles die; each comment "-> sN" below
 // says which slot a tile lands in.  512 threads: warp w owns TMEM lanes 32*(w%4).. and columns
@@ -480,7 +486,9 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       gemm_mm_t<8>(tmem + C_G, a4, a2, ID_MM, !first);
     }
     ph_a ^= 1;
+    B128_MARK(256, 0);
     B128_MMA_WAIT();
+    B128_MARK(256, 1);
     // Vu[I] is consumed (dSu is not yet: the G update still reads it): Ku[I] -> s1 for the dqu product
     if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(s1 + (warp == 9) * kPanelB, &m_ku, &bar_ku2, (warp == 9) * 64, i0, h, b);
     {  // dZ = dA A (1 - A) -> s3 (over the masked T); masked dT -> s0
@@ -498,6 +506,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
       store_row32<T>(s0, kPanelB, row, c0, v);
     }
     B128_SYNC();
+    B128_MARK(256, 2);
 
     // ---- dvu[I] (unscaled) = A^T @ Gb + dT^T @ Qc[I];  dqu[K] += dZ @ Ku[I]
     if (tid == 0) {
@@ -511,6 +520,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     ph_ku2 ^= 1;
     B128_MMA_WAIT();
+    B128_MARK(256, 3);
     // the gate is consumed: Qu[K] -> sA for the dku product
     if (lane == 0 && (warp == 5 || warp == 9)) tma_load_4d(sA + (warp == 9) * kPanelB, &m_qu, &bar_qu2, (warp == 9) * 64, k0, h, b);
     {  // stage dvu[I] over s1|s2 (four fp32 panels, one per chunk group)
@@ -527,6 +537,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     tc_fence_before();
     __syncthreads();
+    B128_MARK(256, 4);
 
     // ---- dku[I] (unscaled) = dZ^T @ Qu[K]
     if (tid == 0) {
@@ -543,6 +554,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     if (issuer) bulk_wait_read0();  // this lane's dvu panel has been read: its slot is free again
     B128_MMA_WAIT();
     __syncthreads();  // orders the issuing lanes' waits before everybody's staging stores
+    B128_MARK(256, 5);
     // The dvu reduce has drained and the last product is done, so the slots of the
     // next step's hand-over tiles are all free: A -> sA, dSu -> s4, masked T -> s3, one 16 KB half per lane
     // of six warps; they arrive while dku is staged.
@@ -569,6 +581,7 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
     }
     tc_fence_before();
     __syncthreads();
+    B128_MARK(256, 6);
   }
   if (issuer) bulk_wait0();
 

@@ -156,8 +156,9 @@ def test_repeatability_config2():
 
 
 def test_repeatability_d128():
-    """Same at dim_head 128 (its three kernels hand tiles over in tensor memory and refill shared-memory
-    panels lane by lane): out, U, dkc and dvc bit for bit; dqc, dqu, dku, dvu are fp32 sums in arrival order."""
+    """Same at dim_head 128 (its kernels hand tiles over in tensor memory, refill shared-memory panels lane by
+    lane, and the two backward kernels pass three tiles per step through global memory): out, U, dqu, dkc and
+    dvc bit for bit; dqc, dku, dvu are fp32 sums in arrival order."""
     from lookahead_keys_attention_b200 import castle_attention_packed, check_status
     packed = _packed(1, 4096, 8, 128, seed=22)
     gen = torch.Generator(device="cuda").manual_seed(6)
@@ -172,6 +173,6 @@ def test_repeatability_d128():
     check_status()
     for out, U, g in res[1:]:
         assert torch.equal(out, res[0][0]) and torch.equal(U, res[0][1])
-        for slot in (4, 5):  # dkc, dvc
+        for slot in (0, 4, 5):  # dqu, dkc, dvc
             assert torch.equal(g[:, :, slot], res[0][2][:, :, slot])
         assert torch.allclose(g.float(), res[0][2].float(), atol=3e-2, rtol=3e-2)
