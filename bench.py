@@ -457,6 +457,50 @@ class ByteLM(torch.nn.Module):
         return torch.nn.functional.cross_entropy(self.logits(self.norm(h)).float().flatten(0, 1), y.flatten())
 
 
+def cfg3_graph_step(lm, ids, c):
+    """The same training step captured once in a CUDA graph and replayed: the eager step is bound by ~400 small
+    launches, not by the GPU.  Returns its own ms per step and tokens/s (or why the capture was not possible)."""
+    from lookahead_keys_attention_b200 import check_status
+    try:
+        opt = torch.optim.Adam(lm.parameters(), lr=1e-4, capturable=True)
+        static_loss = [None]
+
+        def step():
+            opt.zero_grad(set_to_none=True)
+            loss = lm(ids)
+            loss.backward()
+            torch.nn.utils.clip_grad_norm_(lm.parameters(), 0.5)
+            opt.step()
+            static_loss[0] = loss.detach()
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        first = float(static_loss[0])
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+        for _ in range(c["warmup"]):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(c["steps"]):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        check_status()
+        ms = e0.elapsed_time(e1) / c["steps"]
+        return {"ms_per_step": round(ms, 3), "tokens_per_s": round(c["batch"] * c["seq_len"] / (ms * 1e-3), 1),
+                "loss_first_last": [round(first, 4), round(float(static_loss[0]), 4)]}
+    except Exception as e:  # a failed capture must not take the bench line with it
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+
+
 def run_cfg3(dev):
     """8-layer byte LM, bf16 training step (forward, backward, clip, Adam) on batch 16 x 1024 uniform bytes."""
     from lookahead_keys_attention_b200 import check_status
@@ -486,9 +530,11 @@ def run_cfg3(dev):
     torch.cuda.synchronize()
     check_status()
     ms = e0.elapsed_time(e1) / c["steps"]
+    graph = cfg3_graph_step(lm, ids, c)
     return {"metric": "lm_train_tokens_per_s", "value": round(c["batch"] * c["seq_len"] / (ms * 1e-3), 1), "unit": "tokens/s",
             "ms_per_step": round(ms, 3), "steps": c["steps"], "warmup": c["warmup"],
             "loss_first_last": [round(float(losses[0]), 4), round(float(losses[-1]), 4)],
+            "cuda_graph": graph,
             "config": {"workload": f"{c['layers']}-layer byte LM, dim {c['dim']}, {c['heads']} heads x {c['dim_head']}, pre-RMSNorm, 4x GELU FFN, "
                                    f"batch {c['batch']} x {c['seq_len']} uniform bytes, bf16, Adam, clip 0.5 (one step = fwd + bwd + optimizer)"}}
 

@@ -115,7 +115,14 @@ int castle_convert_16bit(int32_t src_dtype, const void* src, void* dst, int64_t 
  * :218-413).  Takes the forward's inputs, `out`, `lse` and `w_state`, and the
  * upstream gradient `dout`; writes the six input gradients (same dtype as the
  * inputs; dqc and dqu already multiplied by `scale`, as at :591-592).  No
- * gradient flows through U (:512-515).  `workspace` holds fp32 accumulators.
+ * gradient flows through U (:512-515).  `workspace` holds fp32 accumulators
+ * and, at dim_head 128, the scratch through which the pass's two kernels hand
+ * three 32 KB tiles per (query block, key block) step: castle_bwd_workspace_bytes
+ * asks for the accumulators plus at most 8 GiB of it, and the (batch, head)
+ * pairs run in chunks of as many as fit.  A smaller workspace is accepted down
+ * to the accumulators plus one pair's tiles (nblk*(nblk+1)/2 * 96 KB, nblk =
+ * ceil(seq_len/128)) and only makes the chunks smaller; the error text of a
+ * refused call states that least size.
  */
 size_t castle_bwd_workspace_bytes(const castle_problem_t* p);
 

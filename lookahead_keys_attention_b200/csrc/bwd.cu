@@ -526,11 +526,19 @@ static int launch_bwd(const BwdParams& p, const CUtensorMap* maps, cudaStream_t 
 
 using namespace castle;
 
-extern "C" size_t castle_bwd_workspace_bytes(const castle_problem_t* p) {
-  if (!p || p->seq_len <= 0) return 0;
+// fp32 accumulators dqc, dvu, dku and delta; at dim_head 128 rounded up so that the tile scratch behind them
+// stays 1 KB aligned
+static size_t bwd_acc_bytes(const castle_problem_t* p) {
   int64_t rows = (int64_t)p->batch * p->heads * p->seq_len;
-  size_t tiles = p->dim_head == 128 ? bwd128_tile_bytes(p->batch * p->heads, (p->seq_len + kBlkB - 1) / kBlkB) : 0;
-  return tiles + (size_t)(rows * (3 * p->dim_head + 1) * sizeof(float));
+  size_t b = (size_t)(rows * (3 * p->dim_head + 1) * sizeof(float));
+  return p->dim_head == 128 ? (b + 1023) & ~(size_t)1023 : b;
+}
+
+extern "C" size_t castle_bwd_workspace_bytes(const castle_problem_t* p) {
+  if (!p || p->seq_len <= 0 || p->batch <= 0 || p->heads <= 0) return 0;
+  const int nblk = (p->seq_len + kBlkB - 1) / kBlkB;
+  size_t tiles = p->dim_head == 128 ? (size_t)bwd128_chunk_pairs(p->batch * p->heads, nblk) * bwd128_pair_bytes(nblk) : 0;
+  return bwd_acc_bytes(p) + tiles;
 }
 
 extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, const castle_tensor_t* kc,
@@ -552,20 +560,28 @@ extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, 
   for (int i = 0; i < 14; ++i)
     if (!tensor_ok(ts[i], p->dtype, names[i], &rc)) return rc;
   if (!lse || !w_state || !status) return reject("castle_bwd: lse, w_state and status must not be null");
-  size_t need = castle_bwd_workspace_bytes(p);
-  if (!workspace || workspace_bytes < need)
-    return reject("castle_bwd: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
+  // dim_head 64: the accumulators.  dim_head 128: the accumulators and the tile hand-over scratch of at least
+  // one (batch, head) pair; the pairs run in chunks of as many as the scratch the caller passed holds.
+  const size_t need = castle_bwd_workspace_bytes(p), acc_bytes = bwd_acc_bytes(p);
+  const size_t pair_bytes = p->dim_head == 128 ? bwd128_pair_bytes(nblk) : 0;
+  const size_t least = p->dim_head == 128 ? acc_bytes + pair_bytes : need;
+  if (!workspace || workspace_bytes < least)
+    return reject("castle_bwd: workspace too small (%zu bytes; castle_bwd_workspace_bytes says %zu, the least that works is %zu)",
+                  workspace_bytes, need, least);
   if (((uintptr_t)workspace) % 16) return reject("castle_bwd: workspace not 16-byte aligned");
 
   BwdParams bp;
   bp.B = p->batch; bp.H = p->heads; bp.N = p->seq_len; bp.nblk = nblk; bp.scale = p->scale;
   bp.lse = lse; bp.w_state = w_state;
   int64_t rows = (int64_t)p->batch * p->heads * p->seq_len;
-  // dim_head 128: the tile hand-over scratch comes first (a multiple of 32 KB, so what follows stays aligned)
-  const size_t tile_bytes = p->dim_head == 128 ? bwd128_tile_bytes(p->batch * p->heads, nblk) : 0;
-  bp.tiles = (uint8_t*)workspace;
-  bp.ntiles = 0; bp.bh0 = 0;
-  bp.acc_dqc = (float*)((uint8_t*)workspace + tile_bytes);
+  // dim_head 128: the tile hand-over scratch follows the accumulators
+  bp.tiles = (uint8_t*)workspace + acc_bytes;
+  bp.ntiles = 0; bp.bh0 = 0; bp.chunk_pairs = 0;
+  if (p->dim_head == 128) {
+    size_t fit = (workspace_bytes - acc_bytes) / pair_bytes;
+    bp.chunk_pairs = (int)(fit < (size_t)(p->batch * p->heads) ? fit : (size_t)(p->batch * p->heads));
+  }
+  bp.acc_dqc = (float*)workspace;
   bp.acc_dvu = bp.acc_dqc + rows * p->dim_head;
   bp.acc_dku = bp.acc_dvu + rows * p->dim_head;
   bp.delta = bp.acc_dku + rows * p->dim_head;
@@ -573,7 +589,8 @@ extern "C" int castle_bwd(const castle_problem_t* p, const castle_tensor_t* qc, 
   bp.dqc = *dqc; bp.dkc = *dkc; bp.dvc = *dvc; bp.dqu = *dqu; bp.dku = *dku; bp.dvu = *dvu;
   bp.status = status;
 #ifdef CASTLE_PHASE_TIMING
-  bp.timing = (long long*)((char*)workspace + need);  // the caller leaves 4 KB beyond the accumulators
+  bp.timing = (long long*)((char*)workspace + need);  // the caller leaves 8 KB beyond what castle_bwd_workspace_bytes asks for
+  if (bp.chunk_pairs > bwd128_chunk_pairs(p->batch * p->heads, nblk)) bp.chunk_pairs = bwd128_chunk_pairs(p->batch * p->heads, nblk);
 #endif
   CUtensorMap maps[10];
   for (int i = 0; i < 7; ++i) {

@@ -616,14 +616,11 @@ castle_bwd128_la_kernel(const BwdParams p, const __grid_constant__ CUtensorMap m
 // Scratch of the tile hand-over: three 32 KB tiles per (query block, key block) step and (batch, head) pair.
 // The pairs run in chunks so that it stays below 8 GiB per launch pair.
 constexpr int64_t kTileScratchLimit = (int64_t)8 << 30;
+size_t bwd128_pair_bytes(int nblk) { return (size_t)nblk * (nblk + 1) / 2 * 3 * kSlot; }
 int bwd128_chunk_pairs(int BH, int nblk) {
-  const int64_t per_pair = (int64_t)nblk * (nblk + 1) / 2 * 3 * kSlot;
-  int64_t n = kTileScratchLimit / per_pair;
+  int64_t n = kTileScratchLimit / (int64_t)bwd128_pair_bytes(nblk);
   if (n < 1) n = 1;
   return (int)(n < BH ? n : BH);
-}
-size_t bwd128_tile_bytes(int BH, int nblk) {
-  return (size_t)bwd128_chunk_pairs(BH, nblk) * ((size_t)nblk * (nblk + 1) / 2) * 3 * kSlot;
 }
 
 template <typename T>
@@ -644,7 +641,7 @@ static int launch_bwd128_t(const BwdParams& p, const CUtensorMap* in, cudaStream
   e = cudaMemsetAsync(p.acc_dqc, 0, (size_t)rows * D * 3 * sizeof(float), st);
   if (e != cudaSuccess) return cuda_fail(e, "castle_bwd memset");
   castle_bwd_delta_kernel<T, D><<<(unsigned)((rows + RPB - 1) / RPB), 256, 0, st>>>(p);
-  const int BH = p.B * p.H, chunk = bwd128_chunk_pairs(BH, p.nblk);
+  const int BH = p.B * p.H, chunk = p.chunk_pairs;
   ev_start(CASTLE_KERNEL_BWD, st);
   for (int bh0 = 0; bh0 < BH; bh0 += chunk) {
     BwdParams q = p;

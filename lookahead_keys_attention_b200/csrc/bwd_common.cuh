@@ -22,6 +22,7 @@ struct BwdParams {
                          // key/value kernel hands to the lookahead kernel
   int64_t ntiles;        // query-block x key-block pairs per (batch, head) pair
   int bh0;               // dim_head 128: first (batch, head) pair of this launch (the pairs run in chunks)
+  int chunk_pairs;       // dim_head 128: pairs per chunk (what the caller's scratch holds)
   castle_tensor_t out, dout;
   castle_tensor_t dqc, dkc, dvc, dqu, dku, dvu;
   int32_t* status;
@@ -79,7 +80,8 @@ __global__ void castle_bwd_finish_kernel(const BwdParams p) {
 }
 
 // dim_head 128 backward (bwd128.cu)
-size_t bwd128_tile_bytes(int BH, int nblk);   // scratch of the tile hand-over between its two kernels
+size_t bwd128_pair_bytes(int nblk);           // tile hand-over scratch of one (batch, head) pair
+int bwd128_chunk_pairs(int BH, int nblk);     // pairs per launch pair that keep the scratch under its limit
 int launch_bwd128(const BwdParams& p, int dtype, const CUtensorMap* in_maps, cudaStream_t st);
 
 }  // namespace castle

@@ -263,6 +263,10 @@ class _CastleAttention(torch.autograd.Function):
         st = status_word(dev)
         prob = CastleProblem(B, H, N, dp, _DTYPES[cdtype], ctx.scale)
         nbytes = int(lib.castle_bwd_workspace_bytes(ctypes.byref(prob)))
+        if dp == 128:
+            # the tile hand-over scratch of the dim_head-128 kernels may be smaller than asked for: the
+            # (batch, head) pairs then run in smaller chunks (the library refuses what holds no pair at all)
+            nbytes = min(nbytes, MAX_WORKSPACE_BYTES)
         ws = _workspace(dev, nbytes)
         args = [_desc(t) for t in (qc, kc, vc, qu, ku, vu, out, do)]
         grads = [_desc(t) for t in (gqc, gkc, gvc, gqu, gku, gvu)]

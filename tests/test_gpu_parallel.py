@@ -153,6 +153,32 @@ def test_backward_matches_oracle_bf16(B, H, N, d):
         _close(g, r, *BF16_TOL, name)
 
 
+def test_backward_d128_pairs_in_chunks(monkeypatch):
+    """dim_head 128: with a workspace that holds the tile hand-over scratch of two (batch, head) pairs only, the
+    five pairs run as three launch pairs (2 + 2 + 1) and the gradients are the same as in one chunk: the
+    owner-written ones bit for bit, the reduced ones to a few ulps; a workspace that holds no pair is refused."""
+    from lookahead_keys_attention_b200 import ops
+    B, H, N, d = 1, 5, 640, 128
+    whole = _grads(B, H, N, d, torch.bfloat16, seed=77)
+    nblk = (N + 127) // 128
+    pair = nblk * (nblk + 1) // 2 * 3 * 32768
+    acc = (B * H * N * (3 * d + 1) * 4 + 1023) // 1024 * 1024
+    monkeypatch.setattr(ops, "MAX_WORKSPACE_BYTES", acc + 2 * pair + 512)
+    ops.release_workspaces()
+    chunked = _grads(B, H, N, d, torch.bfloat16, seed=77)
+    for name, (g, r) in chunked.items():
+        _close(g, r, *BF16_TOL, name)
+        if name in ("dkc", "dvc", "dqu"):
+            assert torch.equal(g, whole[name][0]), name
+        else:
+            assert torch.allclose(g, whole[name][0], atol=3e-2, rtol=3e-2), name
+    monkeypatch.setattr(ops, "MAX_WORKSPACE_BYTES", acc + pair - 1024)
+    ops.release_workspaces()
+    with pytest.raises(RuntimeError, match="workspace too small"):
+        _grads(B, H, N, d, torch.bfloat16, seed=77)
+    ops.release_workspaces()
+
+
 @pytest.mark.parametrize("B,H,N,d", [(1, 2, 256, 64), (1, 1, 200, 32), (1, 1, 260, 128)])
 def test_backward_matches_oracle_fp16(B, H, N, d):
     res = _grads(B, H, N, d, torch.float16, seed=N + d)

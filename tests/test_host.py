@@ -53,6 +53,36 @@ def test_argument_rejection_without_gpu():
     assert lib.castle_bwd_workspace_bytes(ctypes.byref(prob)) == 128 * (3 * 64 + 1) * 4
 
 
+def test_backward_workspace_at_dim_head_128():
+    """Accumulators (rounded up to 1 KB) plus the tile hand-over scratch: 96 KB per (query block, key block) step
+    and (batch, head) pair, for as many pairs as stay under 8 GiB; a workspace below one pair's worth is refused
+    with the least size in the message."""
+    L = _lib()
+    lib = L.load()
+    def acc(B, H, N):
+        return (B * H * N * (3 * 128 + 1) * 4 + 1023) // 1024 * 1024
+    def pair(N):
+        nblk = (N + 127) // 128
+        return nblk * (nblk + 1) // 2 * 3 * 32768
+    for B, H, N in [(1, 1, 1), (1, 5, 640), (2, 3, 1333), (1, 8, 8192)]:
+        prob = L.CastleProblem(B, H, N, 128, L.BF16, 128 ** -0.5)
+        assert lib.castle_bwd_workspace_bytes(ctypes.byref(prob)) == acc(B, H, N) + B * H * pair(N)
+    # config 4's slice: 792 MB per pair, so 10 of the 32 pairs per chunk
+    prob = L.CastleProblem(1, 32, 16384, 128, L.BF16, 128 ** -0.5)
+    assert pair(16384) == 8256 * 98304
+    assert lib.castle_bwd_workspace_bytes(ctypes.byref(prob)) == acc(1, 32, 16384) + 10 * pair(16384)
+    # beyond 8 GiB for a single pair: one pair per chunk
+    prob = L.CastleProblem(1, 4, 65536, 128, L.BF16, 128 ** -0.5)
+    assert lib.castle_bwd_workspace_bytes(ctypes.byref(prob)) == acc(1, 4, 65536) + pair(65536)
+    # refusal (host-side check, before anything touches the device)
+    prob = L.CastleProblem(1, 5, 640, 128, L.BF16, 128 ** -0.5)
+    t = L.CastleTensor(16, 5 * 640 * 128, 640 * 128, 128)
+    r = ctypes.byref(t)
+    least = acc(1, 5, 640) + pair(640)
+    rc = lib.castle_bwd(ctypes.byref(prob), *([r] * 8), 16, 16, *([r] * 6), 1024, least - 1, 16, None)
+    assert rc < 0 and "workspace too small" in L.last_error() and str(least) in L.last_error()
+
+
 def test_new_entry_points_reject_bad_arguments_without_gpu():
     L = _lib()
     lib = L.load()
