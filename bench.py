@@ -236,6 +236,27 @@ def run_ours(args):
     bwd_tflops = rank_f_bwd / (bwd_ms * 1e-3) / 1e12
     fwd_tflops = rank_f_fwd / (fwd_ms * 1e-3) / 1e12
 
+    # ---- the final gather of the sharded path (untimed in `value`): every rank's core output to rank 0
+    gather = None
+    if world > 1 and not weak:
+        from lookahead_keys_attention_b200.sharding import gather_heads
+        with torch.no_grad():
+            out_local = castle_attention_packed(packed.detach(), scale, False)
+            gather_heads(out_local, shard, B, H)   # warm-up (NCCL sets its channels up on first use)
+            barrier(world)
+            ge0, ge1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ge0.record()
+            full_out = gather_heads(out_local, shard, B, H)
+            ge1.record()
+            barrier(world)
+            g_ms = max_over_ranks(ge0.elapsed_time(ge1), world)
+            if rank == 0:
+                ok = bool(torch.equal(full_out[shard.b0:shard.b1, shard.h0:shard.h1], out_local)) and \
+                    bool(torch.isfinite(full_out.float()).all()) and tuple(full_out.shape) == (B, H, N, d)
+                gather = {"ms": round(g_ms, 3), "bytes": full_out.numel() * full_out.element_size(), "checked": ok,
+                          "what": "gather_heads: (batch, head) rectangles of the core output to rank 0 over NCCL"}
+            del full_out, out_local
+
     # ---- end-to-end arm: the module called with host tensors
     group = None
     run_layer = layer
@@ -351,6 +372,8 @@ def run_ours(args):
     }
     if args.no_e2e:
         line["e2e"] = None
+    if gather is not None:
+        line["gather"] = gather
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(steps=2, warmup=1)
     if not args.no_decode:
