@@ -263,10 +263,14 @@ class _CastleAttention(torch.autograd.Function):
         st = status_word(dev)
         prob = CastleProblem(B, H, N, dp, _DTYPES[cdtype], ctx.scale)
         nbytes = int(lib.castle_bwd_workspace_bytes(ctypes.byref(prob)))
-        if dp == 128:
+        if dp == 128 and nbytes > MAX_WORKSPACE_BYTES:
             # the tile hand-over scratch of the dim_head-128 kernels may be smaller than asked for: the
-            # (batch, head) pairs then run in smaller chunks (the library refuses what holds no pair at all)
-            nbytes = min(nbytes, MAX_WORKSPACE_BYTES)
+            # (batch, head) pairs then run in smaller chunks, down to one pair at a time
+            nblk = -(-N // 128)
+            pair = nblk * (nblk + 1) // 2 * 3 * 32768
+            asked_pairs = min(B * H, max(1, (8 << 30) // pair))
+            least = nbytes - (asked_pairs - 1) * pair            # the accumulators and one pair's tiles
+            nbytes = max(least, MAX_WORKSPACE_BYTES)
         ws = _workspace(dev, nbytes)
         args = [_desc(t) for t in (qc, kc, vc, qu, ku, vu, out, do)]
         grads = [_desc(t) for t in (gqc, gkc, gvc, gqu, gku, gvu)]

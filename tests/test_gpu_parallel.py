@@ -156,7 +156,8 @@ def test_backward_matches_oracle_bf16(B, H, N, d):
 def test_backward_d128_pairs_in_chunks(monkeypatch):
     """dim_head 128: with a workspace that holds the tile hand-over scratch of two (batch, head) pairs only, the
     five pairs run as three launch pairs (2 + 2 + 1) and the gradients are the same as in one chunk: the
-    owner-written ones bit for bit, the reduced ones to a few ulps; a workspace that holds no pair is refused."""
+    owner-written ones bit for bit, the reduced ones to a few ulps; with an even smaller bound one pair runs at a time.
+    (That the library itself refuses a workspace that holds no pair is checked on the CPU in test_host.py.)"""
     from lookahead_keys_attention_b200 import ops
     B, H, N, d = 1, 5, 640, 128
     whole = _grads(B, H, N, d, torch.bfloat16, seed=77)
@@ -172,10 +173,12 @@ def test_backward_d128_pairs_in_chunks(monkeypatch):
             assert torch.equal(g, whole[name][0]), name
         else:
             assert torch.allclose(g, whole[name][0], atol=3e-2, rtol=3e-2), name
-    monkeypatch.setattr(ops, "MAX_WORKSPACE_BYTES", acc + pair - 1024)
+    # below one pair's worth the operator still passes the least the library accepts: one pair per chunk
+    monkeypatch.setattr(ops, "MAX_WORKSPACE_BYTES", 1 << 20)
     ops.release_workspaces()
-    with pytest.raises(RuntimeError, match="workspace too small"):
-        _grads(B, H, N, d, torch.bfloat16, seed=77)
+    single = _grads(B, H, N, d, torch.bfloat16, seed=77)
+    for name in ("dkc", "dvc", "dqu"):
+        assert torch.equal(single[name][0], whole[name][0]), name
     ops.release_workspaces()
 
 
