@@ -247,7 +247,9 @@ class _CastleAttention(torch.autograd.Function):
             # the results, so that neither small gradients underflow nor large ones overflow in fp16.
             # Everything stays on the device: no host synchronisation.
             amax = do.detach().abs().amax().float().clamp_min(1e-30)
-            s = torch.exp2(torch.floor(torch.log2(64.0 / amax))).clamp(2.0 ** -24, 2.0 ** 24)
+            # largest power of two <= 64 / amax, from the exponent field (frexp: x = m * 2^e, 0.5 <= m < 1)
+            expo = torch.frexp(64.0 / amax)[1] - 1
+            s = torch.ldexp(torch.ones_like(amax), expo.clamp(-24, 24))
             inv_s = (1.0 / s).reshape(1)
             if do.dtype == torch.bfloat16 and do.is_contiguous() and do.numel() % 8 == 0 and do.data_ptr() % 16 == 0:
                 do = _convert_16bit(do, s.reshape(1))
