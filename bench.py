@@ -444,6 +444,7 @@ def run_cfg4(world, dev, peaks):
     bwd_ms = sum(e[2].elapsed_time(e[3]) for e in ev) / n
     f_fwd, f_bwd = core_flops(B, H, N, d)
     tf = (f_fwd + f_bwd) * world / (ms * 1e-3) / 1e12
+    nblk = -(-N // 128)
     del packed, g
     release_workspaces()
     torch.cuda.empty_cache()
@@ -453,7 +454,13 @@ def run_cfg4(world, dev, peaks):
                        "slices": world},
             "frac_of_tensor_peak": round(tf / (peaks["tflops"] * world), 4),
             "kernels": {"fwd_main_ms": round(fwd_ms, 3), "fwd_main_tflops": round(f_fwd / (fwd_ms * 1e-3) / 1e12, 2),
-                        "bwd_main_ms": round(bwd_ms, 3), "bwd_main_tflops": round(f_bwd / (bwd_ms * 1e-3) / 1e12, 2)}}
+                        "bwd_main_ms": round(bwd_ms, 3), "bwd_main_tflops": round(f_bwd / (bwd_ms * 1e-3) / 1e12, 2)},
+            "roofline": {"kernel": "castle_bwd128_kv_kernel + castle_bwd128_la_kernel", "bound": "tensor",
+                         "achieved": round(f_bwd / (bwd_ms * 1e-3) / 1e12, 2), "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": round(f_bwd / (bwd_ms * 1e-3) / 1e12 / peaks["tflops"], 4),
+                         "traffic": captured_traffic("bwd_d128", B * H * nblk * (nblk + 1) // 2),
+                         "traffic_source": "profiles/ncu_dram_traffic.txt (ncu capture of a smaller launch pair, scaled by (query block, key block) steps)",
+                         "peak_source": f"{peaks['source']} bf16 burst"}}
 
 
 class ByteLM(torch.nn.Module):
